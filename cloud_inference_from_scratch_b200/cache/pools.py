@@ -2,7 +2,8 @@
 
 Layout of a group's pool: ``[layers of the group, 2 (K, V), pages, kv_heads, page_size, head_dim]``;
 for one layer and one of K/V a (page, head) pair is ``page_size * head_dim`` contiguous elements,
-which is what the attention kernels stream.  The reference keeps ``[layers, pages, page_size,
+which is what the attention kernels stream.  A group whose value heads have a size of their own
+keeps two such tensors, one for keys and one for values, each without the axis of 2.  The reference keeps ``[layers, pages, page_size,
 kv_heads, head_dim]`` (src/cloud_engine/cache.py:272-274) and sizes the pool from a byte budget
 (cache.py:266-271); ``plan_groups`` does the same split here.
 """
@@ -19,8 +20,8 @@ def plan_groups(needs: list[Any], element_size: int) -> tuple[list[GroupSpec], d
     """Groups the cache-owning schedule entries by what they need.
 
     Returns the group list and, per owning entry, (group index, layer index inside the group)."""
-    keys: list[tuple[int, int, int]] = []
-    members: dict[tuple[int, int, int], list[int]] = {}
+    keys: list[tuple[int, ...]] = []
+    members: dict[tuple[int, ...], list[int]] = {}
     for need in needs:
         if need.pages is None or need.owner != need.entry:
             continue
@@ -32,13 +33,14 @@ def plan_groups(needs: list[Any], element_size: int) -> tuple[list[GroupSpec], d
     groups: list[GroupSpec] = []
     place: dict[int, tuple[int, int]] = {}
     for index, key in enumerate(keys):
-        window, kv_heads, head_dim = key
+        window, kv_heads, head_dim = key[:3]
+        value_dim = key[3] if len(key) > 3 else head_dim
         entries = members[key]
         groups.append(
             GroupSpec(
                 name=f"window{window}" if window else "full" + (f"-{index}" if index else ""),
                 window=window,
-                bytes_per_token=2 * kv_heads * head_dim * element_size * len(entries),
+                bytes_per_token=kv_heads * (head_dim + value_dim) * element_size * len(entries),
             )
         )
         for layer, entry in enumerate(entries):
@@ -110,24 +112,30 @@ class CachePools:
 
         self.page_size = page_size
         self.pools: list[Any] = []
-        shapes: dict[int, tuple[int, int]] = {}
+        shapes: dict[int, tuple[int, int, int]] = {}
         layers_in: dict[int, int] = {}
         for need in needs:
             if need.entry in place:
                 group, layer = place[need.entry]
-                shapes[group] = (need.pages.kv_heads, need.pages.head_dim)
+                shapes[group] = (need.pages.kv_heads, need.pages.head_dim, need.pages.value_size)
                 layers_in[group] = max(layers_in.get(group, 0), layer + 1)
         for index, _ in enumerate(groups):
             if index not in shapes:
                 self.pools.append(None)
                 continue
-            kv_heads, head_dim = shapes[index]
-            self.pools.append(
-                torch.zeros(
-                    (layers_in[index], 2, pages_per_group[index], kv_heads, page_size, head_dim),
-                    dtype=dtype, device=device,
+            kv_heads, head_dim, value_dim = shapes[index]
+            if value_dim == head_dim:
+                self.pools.append(
+                    torch.zeros(
+                        (layers_in[index], 2, pages_per_group[index], kv_heads, page_size, head_dim),
+                        dtype=dtype, device=device,
+                    )
                 )
-            )
+            else:   # keys and values of different sizes: a tensor each
+                self.pools.append(tuple(
+                    torch.zeros((layers_in[index], pages_per_group[index], kv_heads, page_size, size),
+                                dtype=dtype, device=device)
+                    for size in (head_dim, value_dim)))
         self.pages_per_group = list(pages_per_group)
         self.states: dict[int, Any] = {}
         for need in needs:
@@ -142,7 +150,8 @@ class CachePools:
             if need.pages is not None:
                 group, layer = place[need.owner]
                 pool = self.pools[group]
-                kv = KVLayerView(group=group, k=pool[layer, 0], v=pool[layer, 1],
+                keys, values = (pool[0][layer], pool[1][layer]) if isinstance(pool, tuple) else (pool[layer, 0], pool[layer, 1])
+                kv = KVLayerView(group=group, k=keys, v=values,
                                  num_pages=pages_per_group[group], page_size=page_size)
             self.bindings.append(
                 LayerBinding(entry=need.entry, owns_cache=need.owner == need.entry, kv=kv,
@@ -155,5 +164,6 @@ class CachePools:
                 state[slot].zero_()
 
     def bytes_held(self) -> int:
-        total = sum(p.numel() * p.element_size() for p in self.pools if p is not None)
+        total = sum(t.numel() * t.element_size() for p in self.pools if p is not None
+                    for t in (p if isinstance(p, tuple) else (p,)))
         return total + sum(s.numel() * s.element_size() for s in self.states.values())

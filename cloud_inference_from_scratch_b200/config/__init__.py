@@ -8,11 +8,12 @@ from .registry import (
     resolve_config,
     resolve_model,
 )
+from .zisesun_config import ZisesunConfig
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 __all__ = [
     "Architecture", "ConfigError", "EngineConfig", "LayerSpec", "ModelSpec", "PartSpec",
-    "Qwen2Config", "ScheduleEntry", "architecture_for", "build_config", "read_config_json",
+    "Qwen2Config", "ScheduleEntry", "ZisesunConfig", "architecture_for", "build_config", "read_config_json",
     "register_architecture", "registered_architectures", "resolve_config", "resolve_model",
     "validate_config", "with_overrides",
 ]

@@ -1,8 +1,8 @@
 """One registry from an architecture's name to its configuration class and its model description.
 
 The reference has no registry, only a ``model_type`` check (src/cloud_engine/model.py:61-63).
-Here ``config.json``'s ``architectures[0]`` (or, when that key is absent, its
-``model_type``) selects an entry; an entry is a function from the raw config.json
+Here ``config.json``'s ``architectures[0]`` (or its ``architecture``, a single name; or, when
+both keys are absent, its ``model_type``) selects an entry; an entry is a function from the raw config.json
 dictionary to a typed configuration and a function from that configuration to a
 ``ModelSpec``.  The engine, the loader, the random-weights writer and the replay
 program all resolve a model folder through ``resolve_model``.
@@ -49,6 +49,8 @@ def registered_architectures() -> tuple[str, ...]:
 
 def architecture_for(raw: dict[str, Any]) -> Architecture:
     names = raw.get("architectures")
+    if not names and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]      # a single name under the singular key
     if names:
         name = names[0]
         if name not in _ARCHITECTURES:

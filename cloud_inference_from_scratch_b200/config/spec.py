@@ -111,12 +111,19 @@ class ModelSpec:
     embedding_scale: float = 1.0      # the gathered embedding rows are multiplied by this
     logit_scale: float = 1.0          # logits = softcap * tanh(head(x) * scale / softcap), or head(x) * scale
     logit_softcap: float = 0.0        # 0: no soft cap
+    # a learned vector per position [max_positions, hidden] added to the embedding rows (None: none)
+    position_tensor: str | None = None
+    # copies of the residual stream that the blocks keep side by side (hyper-connections); all start
+    # as the embedding rows and their sum is what the final norm reads
+    residual_streams: int = 1
 
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
         if self.logit_softcap < 0:
             raise ValueError("logit_softcap must be >= 0")
+        if self.residual_streams < 1:
+            raise ValueError("residual_streams must be >= 1")
         for index, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule entry {index} names layer {entry.layer}, which does not exist")

@@ -8,6 +8,10 @@
 // running-maximum softmax, out = sum(p v) / sum(p); query head h reads kv head h / (Hq/Hkv).
 // Keys are visited in blocks of 32 counted from the first visible key, so the result for a
 // token depends only on its request's keys, not on the batch, the cut or the pages used.
+//
+// Two generalisations (cie_attention_generic_ex): value heads of a size of their own (`vdim`), and
+// a logarithmic distance penalty per query head, s = (q.k) * scale - r1[h] * log(1 + r2[h] * (p - j))
+// for a key at position j (r1 == nullptr: none).
 #include "common.cuh"
 
 #include <cfloat>
@@ -25,8 +29,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                          const int* __restrict__ positions, const int* __restrict__ request_of_token,
                          const int* __restrict__ table, int table_width, int num_pages, int tokens,
-                         int q_heads, int kv_heads, int dim, int page_size, float scale, int window,
-                         int* err) {
+                         int q_heads, int kv_heads, int dim, int vdim, int page_size, float scale, int window,
+                         const float* __restrict__ r1, const float* __restrict__ r2, int* err) {
   __shared__ float q_s[kWarps][kMaxDim];
   __shared__ float p_s[kWarps][32];
   __shared__ long long off_s[kWarps][32];
@@ -42,6 +46,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   const int* row = table + (size_t)request * table_width;
   const int length = pos + 1;
   const int first = (window > 0 && length > window) ? length - window : 0;
+  const float penalty = r1 ? r1[h] : 0.f, reach = r1 ? r2[h] : 0.f;
 
   const T* qv = q + (size_t)t * q_stride + (size_t)h * dim;
   for (int d = lane; d < dim; d += 32) q_s[warp][d] = to_float(qv[d]);
@@ -62,15 +67,16 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
       if (page < 0 || page >= num_pages) {
         atomicOr(err, kErrBadPage);
       } else {
-        offset = (((long long)page * kv_heads + kvh) * page_size + key % page_size) * dim;
+        offset = ((long long)page * kv_heads + kvh) * page_size + key % page_size;   // slot; times dim or vdim
       }
     }
     float s = -FLT_MAX;
     if (offset >= 0) {
-      const T* kr = k_pool + offset;
+      const T* kr = k_pool + offset * dim;
       float dot = 0.f;
       for (int d = 0; d < dim; ++d) dot = fmaf(q_s[warp][d], to_float(kr[d]), dot);
       s = dot * scale;
+      if (r1) s -= penalty * log1pf(reach * (float)(pos - key));
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = offset >= 0 ? expf(s - m_new) : 0.f;
@@ -87,21 +93,21 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
       const long long o = off_s[warp][j];
       if (o < 0) continue;
       const float pj = p_s[warp][j];
-      const T* vr = v_pool + o;
+      const T* vr = v_pool + o * vdim;
 #pragma unroll
       for (int i = 0; i < kMaxDim / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < dim) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
+        if (d < vdim) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
       }
     }
     __syncwarp();
   }
-  T* o = out + (size_t)t * out_stride + (size_t)h * dim;
+  T* o = out + (size_t)t * out_stride + (size_t)h * vdim;
   const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < kMaxDim / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < dim) o[d] = from_float<T>(acc[i] * inv);
+    if (d < vdim) o[d] = from_float<T>(acc[i] * inv);
   }
 }
 
@@ -110,32 +116,46 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 using namespace cie;
 
 // q: rows of q_stride elements, query head h of token t at q[t*q_stride + h*dim].
-// out: [tokens, out_stride], head h at column h*dim.  Pools: [pages][kv_heads][page_size][dim].
-extern "C" int cie_attention_generic(const void* q, int q_stride, void* out, int out_stride,
-                                     const void* k_pool, const void* v_pool, const int* positions,
-                                     const int* request_of_token, const int* table, int table_width,
-                                     int num_pages, int tokens, int q_heads, int kv_heads, int dim,
-                                     int page_size, float scale, int window, int dtype, int* err,
-                                     void* stream) {
+// out: [tokens, out_stride], head h at column h*vdim.  Pools: [pages][kv_heads][page_size][dim or vdim].
+extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* k_pool, const void* v_pool, const int* positions,
+                                        const int* request_of_token, const int* table, int table_width,
+                                        int num_pages, int tokens, int q_heads, int kv_heads, int dim,
+                                        int vdim, int page_size, float scale, int window,
+                                        const float* r1, const float* r2, int dtype, int* err,
+                                        void* stream) {
   if (tokens <= 0) return 0;
-  if (dim > kMaxDim || dim < 1) CIE_FAIL("attention_generic: head size %d is outside 1..%d", dim, kMaxDim);
+  if (dim > kMaxDim || dim < 1 || vdim > kMaxDim || vdim < 1)
+    CIE_FAIL("attention_generic: head sizes %d / %d are outside 1..%d", dim, vdim, kMaxDim);
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_generic: %d query heads do not divide over %d kv heads", q_heads, kv_heads);
   if (page_size < 1) CIE_FAIL("attention_generic: page size %d", page_size);
+  if ((r1 == nullptr) != (r2 == nullptr)) CIE_FAIL("attention_generic: the distance penalty needs both of its vectors");
   const long long items = (long long)tokens * q_heads;
   const int blocks = (int)((items + kWarps - 1) / kWarps);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kFloat32) {
     CIE_LAUNCH("attention_generic", attention_generic_kernel<float>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
-        positions, request_of_token, table, table_width, num_pages, tokens, q_heads, kv_heads, dim,
-        page_size, scale, window, err);
+        positions, request_of_token, table, table_width, num_pages, tokens, q_heads, kv_heads, dim, vdim,
+        page_size, scale, window, r1, r2, err);
   } else if (dtype == kBFloat16) {
     CIE_LAUNCH("attention_generic", attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
         (const __nv_bfloat16*)v_pool, positions, request_of_token, table, table_width, num_pages, tokens,
-        q_heads, kv_heads, dim, page_size, scale, window, err);
+        q_heads, kv_heads, dim, vdim, page_size, scale, window, r1, r2, err);
   } else {
     CIE_FAIL("attention_generic: unknown element type code %d", dtype);
   }
   return 0;
+}
+
+extern "C" int cie_attention_generic(const void* q, int q_stride, void* out, int out_stride,
+                                     const void* k_pool, const void* v_pool, const int* positions,
+                                     const int* request_of_token, const int* table, int table_width,
+                                     int num_pages, int tokens, int q_heads, int kv_heads, int dim,
+                                     int page_size, float scale, int window, int dtype, int* err,
+                                     void* stream) {
+  return cie_attention_generic_ex(q, q_stride, out, out_stride, k_pool, v_pool, positions, request_of_token,
+                                  table, table_width, num_pages, tokens, q_heads, kv_heads, dim, dim,
+                                  page_size, scale, window, nullptr, nullptr, dtype, err, stream);
 }

@@ -56,14 +56,17 @@ def main(argv: list[str] | None = None) -> int:
     import numpy as np
 
     from .. import models, parts  # noqa: F401  (registries)
+    from ..config.registry import resolve_model
     from .core import build_core
     from .step import StepEntry
 
     page = args.page_size
     num_pages = -(-args.max_tokens // page)
+    # one request can hold the whole pool, but never more positions than the model has
+    longest = min(max(page, num_pages * page), resolve_model(args.model)[2].max_positions)
     core = build_core(
         args.model, dtype=args.dtype, device=args.device, page_size=page, num_pages=num_pages,
-        max_requests=MAX_LIVE_REQUESTS, max_model_len=max(page, num_pages * page),
+        max_requests=MAX_LIVE_REQUESTS, max_model_len=longest,
     )
     step_fn = core.step
     live: set[str] = set()

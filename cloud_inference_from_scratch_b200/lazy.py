@@ -76,6 +76,20 @@ class NormedInput:
         return tuple(self.accumulated.scaled.shape)
 
 
+class StreamUpdate:
+    """A sublayer's result ``y`` [T, H] that has not been written to the residual streams yet: every
+    stream t becomes ``sum_s mix[s, t] * stream_s + out[t] * y``.  ``mix`` None is the identity and
+    ``out`` None all ones, which with one stream is the plain residual add.  Whoever reads the
+    streams next (a norm) applies it first, in the same kernel."""
+
+    def __init__(self, y: Any, mix: Any = None, out: Any = None) -> None:
+        self.y, self.mix, self.out = y, mix, out
+
+    @property
+    def shape(self) -> tuple[int, ...]:
+        return tuple(self.y.shape)
+
+
 class GateUpWeight:
     """Stacked gate and up matrices [2I, H].  ``block`` == I: all gate rows, then all up rows.
     ``block`` < I: rows interleaved in blocks (``block`` gate rows, the matching ``block`` up

@@ -7,6 +7,11 @@ description, not a class.  The forward pass is the reference's
 gather embeddings into the float32 residual stream, run the schedule, normalise only
 the rows whose logits are wanted (the reference normalises all rows and then selects,
 model.py:221-225), multiply by the head and return float32 logits.
+
+Beyond the reference: a description may ask for a learned vector per position that is added to the
+embedding rows (``position_tensor``) and for several copies of the residual stream side by side
+(``residual_streams``, [T, streams * H]); the blocks of such a model read and write the copies and
+the final norm reads their sum.
 """
 
 from __future__ import annotations
@@ -100,6 +105,7 @@ class DecoderModel:
             getattr(part, "kernels_through_ops", False)
             for layer in self.layers for part in [layer.block, *layer.parts.values()])
         self.embedding: Any = None
+        self.position_table: Any = None
         self.head: Any = None
         self.runtime: Any = None
 
@@ -112,6 +118,8 @@ class DecoderModel:
         }
         if spec.head_tensor != spec.embedding_tensor:
             table[spec.head_tensor] = TensorSpec((spec.vocab_size, spec.hidden_size))
+        if spec.position_tensor:
+            table[spec.position_tensor] = TensorSpec((spec.max_positions, spec.hidden_size))
         for layer in self.layers:
             for prefix, part in layer.named_parts():
                 for name, tensor in part.tensor_specs().items():
@@ -144,6 +152,8 @@ class DecoderModel:
         self.runtime = runtime
         spec = self.spec
         self.embedding = runtime.ops.prepare_weight(tensors(spec.embedding_tensor))
+        self.position_table = (runtime.ops.prepare_weight(tensors(spec.position_tensor))
+                               if spec.position_tensor else None)
         self.head = (
             self.embedding
             if spec.head_tensor == spec.embedding_tensor
@@ -164,9 +174,15 @@ class DecoderModel:
 
         rt = self.runtime
         spec = self.spec
-        residual = rt.workspace.get("residual", ctx.num_tokens, spec.hidden_size, torch.float32)
-        rt.ops.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale)
-        sink = rt.ops.residual_sink(residual) if self.norms_accept_accumulated else None
+        streams = spec.residual_streams
+        residual = rt.workspace.get("residual", ctx.num_tokens, spec.hidden_size * streams, torch.float32)
+        if streams > 1 or self.position_table is not None:
+            # the stream copies lie side by side in a token's row; a learned position vector is added
+            rt.ops.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale,
+                             positions=ctx.positions, position_table=self.position_table, streams=streams)
+        else:
+            rt.ops.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale)
+        sink = rt.ops.residual_sink(residual) if self.norms_accept_accumulated and streams == 1 else None
         ctx.residual_sink = sink
         pending = None
         recorded = self.records_programs and sink is not None and rt.ops.begin_program(ctx)

@@ -15,7 +15,7 @@ import os
 from ctypes import c_float, c_int, c_void_p
 from typing import Any
 
-from ..lazy import Accumulated, GateUpWeight, NormedInput, Partials, ResidualSink  # noqa: F401  (re-exported)
+from ..lazy import Accumulated, GateUpWeight, NormedInput, Partials, ResidualSink, StreamUpdate  # noqa: F401  (re-exported)
 from .build import load_library
 
 F32, BF16 = 0, 1
@@ -102,6 +102,14 @@ class Ops:
             "cie_attention_generic",
             [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, f, i, i, v, v],
         )
+        self._attention_generic_ex = ag.function(
+            "cie_attention_generic_ex",
+            [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v],
+        )
+        # libraries that only some models need are built and loaded when a part first asks for them
+        self._streams_lib = None
+        self._lightning_lib = None
+        self._moe_lib = None
         self._sample = None   # sampling.cu is built when something is first sampled
         self._tensor_gemm = None
         self._fold_gemm_held = None
@@ -219,11 +227,21 @@ class Ops:
             raise KernelError("device error word set: " + "; ".join(faults))
 
     # ------------------------------------------------------------------ kernels
-    def embedding(self, token_ids: Any, table: Any, residual: Any, scale: float = 1.0) -> None:
-        """residual[t] = table[token_ids[t]] * scale, float32."""
+    def embedding(self, token_ids: Any, table: Any, residual: Any, scale: float = 1.0,
+                  positions: Any = None, position_table: Any = None, streams: int = 1) -> None:
+        """residual[t] = table[token_ids[t]] * scale (+ position_table[positions[t]]), float32, in each
+        of ``streams`` side-by-side copies ([T, streams * H])."""
         self._flush()
-        tokens, hidden = residual.shape
+        tokens = residual.shape[0]
+        hidden = residual.shape[1] // streams
         self.launches += 1
+        if position_table is not None or streams > 1:
+            self._load_streams()
+            self._embedding_streams(_ptr(token_ids), _ptr(positions), _ptr(table), _ptr(position_table),
+                                    _ptr(residual), tokens, hidden, table.shape[0],
+                                    0 if position_table is None else position_table.shape[0], streams,
+                                    float(scale), self._code_of(table), _ptr(self.error_word), self.stream)
+            return
         self._embedding(_ptr(token_ids), _ptr(table), _ptr(residual), tokens, hidden,
                         table.shape[0], float(scale), self._code_of(table), _ptr(self.error_word), self.stream)
 
@@ -256,6 +274,145 @@ class Ops:
         else:
             self._add_rmsnorm(_ptr(residual), _ptr(update), 0, 0, None, _ptr(gain), _ptr(out),
                               _ptr(rows), count, hidden, eps, self._code_of(out), self.stream)
+
+    # ------------------------------------------------------------------ residual streams
+    def _load_streams(self) -> None:
+        if self._streams_lib is None:
+            v, i, f = c_void_p, c_int, c_float
+            lib = _Lib(load_library("streams.cu"))
+            self._embedding_streams = lib.function("cie_embedding_streams", [v, v, v, v, v, i, i, i, i, i, f, i, v, v])
+            self._stream_norm = lib.function("cie_stream_norm", [v, i, v, i, v, v, v, v, i, v, v, i, i, f, i, v])
+            self._norm_kv_write = lib.function(
+                "cie_norm_kv_write", [v, v, v, i, v, v, v, i, i, v, v, v, v, i, i, i, i, i, i, i, i, f, i, i, v, v])
+            self._streams_lib = lib
+
+    def stream_norm(self, residual: Any, streams: int, update: Any, read: Any, gain: Any, eps: float,
+                    out: Any, rows: Any = None) -> None:
+        """The boundary between two sublayers over ``streams`` copies of the residual stream
+        (``residual``: float32 [T, streams * H]): applies ``update`` (a ``StreamUpdate``, a plain
+        tensor to add to every stream, or None) in place, reads ``sum_t read[t] * stream_t`` (``read``
+        None: the plain sum) and writes its RMS norm times ``gain`` (a vector [H] or one number) to
+        ``out``.  With ``rows`` only those token rows are read and nothing is written back."""
+        self._flush()
+        self._load_streams()
+        if isinstance(update, Accumulated):
+            update = None
+        if isinstance(update, Partials):
+            update = self.resolve(update, self.torch.empty(update.shape, dtype=self.torch.float32, device=self.device))
+        if update is not None and not isinstance(update, StreamUpdate):
+            update = StreamUpdate(update)
+        if update is not None and isinstance(update.y, Partials):
+            update.y = self.resolve(update.y, self.torch.empty(update.y.shape, dtype=self.torch.float32, device=self.device))
+        count, hidden = out.shape
+        y = update.y if update is not None else None
+        self.launches += 1
+        self._stream_norm(_ptr(residual), streams, _ptr(y), self._code_of(y) if y is not None else 0,
+                          _ptr(update.mix) if update is not None else None,
+                          _ptr(update.out) if update is not None else None, _ptr(read), _ptr(gain),
+                          1 if gain.numel() == 1 else 0, _ptr(out), _ptr(rows), count, hidden, float(eps),
+                          self._code_of(out), self.stream)
+
+    def norm_kv_write(self, qkv: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int, dim: int, vdim: int,
+                      q_gain: Any, k_gain: Any, value_norm: bool, eps: float, q_buffer: Any,
+                      write_cache: bool = True) -> Any:
+        """q and k of every token divided by the root mean square of their whole projection and
+        multiplied by a gain vector (``q_gain`` None: left as they are), every value head divided by
+        its own root mean square (``value_norm``); q goes to ``q_buffer``, k and v into the pages.
+        ``qkv`` is a tensor [T, (Hq + Hkv) * dim + Hkv * vdim] or ``Partials`` with its bias pending."""
+        self._flush()
+        self._load_streams()
+        bias = None
+        if isinstance(qkv, Partials):
+            if qkv.splits:
+                qkv = self.resolve(qkv, self.torch.empty(qkv.shape, dtype=self.dtype, device=self.device))
+            else:
+                qkv, bias = qkv.data, qkv.bias
+        table = ctx.block_tables[kv.group]
+        self.launches += 1
+        self._norm_kv_write(_ptr(qkv), _ptr(bias), _ptr(q_buffer), q_buffer.shape[1], _ptr(ctx.positions),
+                            _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, _ptr(kv.k),
+                            _ptr(kv.v), _ptr(q_gain), _ptr(k_gain), qkv.shape[0], q_heads, kv_heads, dim, vdim,
+                            kv.page_size, 1 if q_gain is not None else 0, 1 if value_norm else 0, float(eps),
+                            1 if write_cache else 0, self._code_of(qkv), _ptr(self.error_word), self.stream)
+        return q_buffer
+
+    # ------------------------------------------------------------------ linear attention with decay
+    def _load_lightning(self) -> None:
+        if self._lightning_lib is None:
+            v, i, f = c_void_p, c_int, c_float
+            lib = _Lib(load_library("lightning.cu"))
+            self._lightning_scan = lib.function("cie_lightning_scan", [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, v, v])
+            self._lightning_gate_norm = lib.function("cie_lightning_gate_norm", [v, i, v, i, v, v, i, i, f, i, v])
+            self._lightning_lib = lib
+
+    def lightning_scan(self, proj: Any, out: Any, state: Any, decay: Any, ctx: Any, heads: int, dim: int,
+                       vdim: int) -> None:
+        """Runs S <- decay * S + k v^T, o = S^T q over every request's new tokens from the state in
+        its slot (``state``: float32 [slots, heads, dim, vdim]).  ``proj`` rows are [q | k | v | ...]
+        before their SiLU; ``out`` is float32 [T, heads * vdim]."""
+        self._flush()
+        self._load_lightning()
+        self.launches += 1
+        self._lightning_scan(_ptr(proj), proj.stride(0), _ptr(out), out.stride(0), _ptr(state), _ptr(decay),
+                             _ptr(ctx.query_start), _ptr(ctx.slots), _ptr(ctx.request_active), ctx.num_requests,
+                             heads, dim, vdim, state.shape[0], self._code_of(proj), _ptr(self.error_word),
+                             self.stream)
+
+    def lightning_gate_norm(self, o: Any, gate: Any, gain: Any, eps: float, out: Any) -> None:
+        """out = gain * o / rms(o) * sigmoid(gate), the norm over the whole row (all heads together);
+        ``gate`` is a view of columns of the projection (its row stride is used)."""
+        self._flush()
+        self._load_lightning()
+        self.launches += 1
+        self._lightning_gate_norm(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0), _ptr(gain), _ptr(out),
+                                  out.shape[0], out.shape[1], float(eps), self._code_of(out), self.stream)
+
+    # ------------------------------------------------------------------ routed experts
+    def _load_moe(self) -> None:
+        if self._moe_lib is None:
+            v, i = c_void_p, c_int
+            lib = _Lib(load_library("moe.cu"))
+            self._moe_route = lib.function("cie_moe_route", [v, v, v, v, v, v, v, v, v, v, v, i, i, i, i, i, i, v])
+            self._moe_gate_up_simt = lib.function("cie_moe_gate_up_simt", [v, v, v, v, v, v, v, i, i, i, i, i, i, v])
+            self._moe_down_simt = lib.function("cie_moe_down_simt", [v, v, v, v, v, v, i, i, i, i, i, i, v])
+            self._moe_combine = lib.function("cie_moe_combine", [v, v, v, i, i, i, i, v])
+            self.moe_row_tile = int(lib.handle.cie_moe_row_tile())
+            self._moe_lib = lib
+
+    def routed_experts(self, x: Any, router: Any, correction: Any, w_gate: Any, w_up: Any, w_down: Any,
+                       top: int, renormalize: bool, out: Any, workspace: Any) -> Any:
+        """out[t] = sum over the ``top`` chosen experts e of score_e * down_e(SiLU(gate_e x) * up_e x).
+        ``router`` float32 [E, H]; ``w_gate``/``w_up`` [E, F, H]; ``w_down`` [E, H, F]; ``out`` float32
+        or the activation type."""
+        self._flush()
+        self._load_moe()
+        torch = self.torch
+        tokens, hidden = x.shape
+        experts, ff = w_gate.shape[0], w_gate.shape[1]
+        pairs = tokens * top
+        ids = workspace.get("moe.ids", tokens, top, torch.int32)
+        weights = workspace.get("moe.weights", tokens, top, torch.float32)
+        place_to_pair = workspace.get("moe.places", tokens, top, torch.int32)
+        # counts, offsets, cursors, the tile count and the tile list (three numbers a tile; at most one
+        # tile per 64 pairs plus one per expert) share one integer buffer that holds them for any
+        # number of tokens
+        plan = workspace.get("moe.plan", tokens, 6 * experts + 8 + (3 * top + 63) // 64, torch.int32).view(-1)
+        counts, offsets, cursors = plan[:experts], plan[experts:2 * experts + 1], plan[2 * experts + 1:3 * experts + 1]
+        tile_count, tiles = plan[3 * experts + 1:3 * experts + 2], plan[3 * experts + 2:]
+        assert tiles.numel() >= 3 * (-(-pairs // self.moe_row_tile) + experts)
+        act = workspace.get("moe.act", tokens, top * ff, self.dtype)
+        rows = workspace.get("moe.rows", tokens, top * hidden, torch.float32)
+        code = self._code_of(x)
+        self.launches += 5
+        self._moe_route(_ptr(x), _ptr(router), _ptr(correction), _ptr(ids), _ptr(weights), _ptr(counts),
+                        _ptr(offsets), _ptr(cursors), _ptr(place_to_pair), _ptr(tiles), _ptr(tile_count), tokens,
+                        hidden, experts, top, 1 if renormalize else 0, code, self.stream)
+        self._moe_gate_up_simt(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(act), _ptr(place_to_pair), _ptr(tiles),
+                               _ptr(tile_count), tokens, top, experts, ff, hidden, code, self.stream)
+        self._moe_down_simt(_ptr(act), _ptr(w_down), _ptr(rows), _ptr(place_to_pair), _ptr(tiles),
+                            _ptr(tile_count), tokens, top, experts, ff, hidden, code, self.stream)
+        self._moe_combine(_ptr(rows), _ptr(weights), _ptr(out), tokens, hidden, top, self._code_of(out), self.stream)
+        return out
 
     def stream_plan(self, m: int, n: int, k: int, allow_partials: bool) -> tuple[int, int] | None:
         """(weight rows per CTA, splits along K) for the streaming kernel, or None if the shape
@@ -599,10 +756,21 @@ class Ops:
         self.attention_generic(qkv, out, ctx, kv, q_heads, kv_heads, head_dim, scale, window)
 
     def attention_generic(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int,
-                          kv_heads: int, head_dim: int, scale: float, window: int) -> None:
+                          kv_heads: int, head_dim: int, scale: float, window: int,
+                          value_dim: int | None = None, distance: Any = None) -> None:
+        """``value_dim``: size of a value head when it is not ``head_dim``; ``distance``: (r1, r2),
+        float32 [q_heads] each, of the penalty r1 * log(1 + r2 * (query position - key position))."""
         self._flush()
         table = ctx.block_tables[kv.group]
         self.launches += 1
+        if distance is not None or (value_dim or head_dim) != head_dim:
+            r1, r2 = distance if distance is not None else (None, None)
+            self._attention_generic_ex(_ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k),
+                                       _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token),
+                                       _ptr(table), table.shape[1], kv.num_pages, qkv.shape[0], q_heads,
+                                       kv_heads, head_dim, value_dim or head_dim, kv.page_size, scale, window,
+                                       _ptr(r1), _ptr(r2), self._code_of(qkv), _ptr(self.error_word), self.stream)
+            return
         self._attention_generic(_ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k),
                                 _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token),
                                 _ptr(table), table.shape[1], kv.num_pages, qkv.shape[0], q_heads,

@@ -1,7 +1,8 @@
-from . import attention, block, mlp, norm, rotary  # noqa: F401  (registers the built-in parts)
+from . import attention, block, connection, lightning, mlp, norm, rotary, routed  # noqa: F401  (registers the built-in parts)
 from .base import (
     Block,
     CacheSpec,
+    Connection,
     FeedForward,
     Mixer,
     Norm,
@@ -16,6 +17,6 @@ from .base import (
 )
 
 __all__ = [
-    "Block", "CacheSpec", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding",
+    "Block", "CacheSpec", "Connection", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding",
     "StateSpec", "TensorSpec", "build_part", "part_class", "register_part", "registered_parts",
 ]

@@ -11,6 +11,23 @@ Here q, k and v come from ONE matrix product with the three weights stacked, the
 rotation is fused with the write of k and v into the pages, and attention reads the
 pages directly through the block table.  ``window`` > 0 limits a query at position p
 to keys p-window+1..p.
+
+Options beyond the reference, each a constant of the part so that any description may use it:
+
+* ``value_dim``: value heads of a size of their own (the pages then keep keys and values in two
+  tensors);
+* ``qk_norm="projection"``: q and k are each divided by the root mean square of their whole
+  projection (all heads together, before the split into heads) and multiplied by a stored gain
+  vector of that size; keys are cached so;
+* ``value_norm``: every value head is divided by its own root mean square (no gain) before it is
+  cached;
+* ``distance_penalty``: the score of query position i and key position j is lowered by
+  ``r1_h * ln(1 + r2_h * (i - j))`` with two stored numbers per query head;
+* ``position=None``: no rotation;
+* ``names``: the tensor names, where a model stores them under others.
+
+With any of the first four the layer runs product -> norms + cache write -> attention -> output
+projection with the kernels of those options; scores, softmax and norms are float32.
 """
 
 from __future__ import annotations
@@ -32,6 +49,12 @@ class Attention(Mixer):
         position: PartSpec | None,
         window: int = 0,
         scale: float | None = None,
+        value_dim: int | None = None,
+        qk_norm: str | None = None,
+        value_norm: bool = False,
+        distance_penalty: bool = False,
+        norm_eps: float = 1e-6,
+        names: dict[str, str] | None = None,
     ) -> None:
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
@@ -46,10 +69,31 @@ class Attention(Mixer):
         self.scale *= float(getattr(self.position, "attention_factor", 1.0))
         self.q_width = self.num_heads * self.head_dim
         self.kv_width = self.num_kv_heads * self.head_dim
-        self.qkv_width = self.q_width + 2 * self.kv_width
+        self.value_dim = int(value_dim) if value_dim else self.head_dim
+        self.v_width = self.num_kv_heads * self.value_dim
+        self.out_width = self.num_heads * self.value_dim
+        self.qkv_width = self.q_width + self.kv_width + self.v_width
+        if qk_norm not in (None, "projection"):
+            raise ValueError(f"qk_norm must be None or 'projection', got {qk_norm!r}")
+        self.qk_norm = qk_norm
+        self.value_norm = bool(value_norm)
+        self.distance_penalty = bool(distance_penalty)
+        self.norm_eps = float(norm_eps)
+        # the options that the rotary kernels and the tensor-core attention kernels do not know
+        self.general = bool(self.qk_norm or self.value_norm or self.distance_penalty
+                            or self.value_dim != self.head_dim)
+        if self.general and self.position is not None:
+            raise ValueError("q/k norm, value norm, distance penalty and a value size of its own are built "
+                             "for attention without rotation")
+        self.names = {key: key for key in ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
+                                           "q_proj.bias", "k_proj.bias", "v_proj.bias", "q_norm", "k_norm",
+                                           "r1", "r2")}
+        self.names.update(names or {})
 
     @property
     def plan_key(self):
+        if self.general:      # its attention kernel walks the batch itself: no work lists
+            return None
         return ("attention", self.num_heads // self.num_kv_heads)
 
     def plan(self, host, cache):
@@ -57,19 +101,27 @@ class Attention(Mixer):
         return self.runtime.ops.plan_attention(host, self.num_heads // self.num_kv_heads)
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window)
+        return CacheSpec(kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window,
+                         value_dim=0 if self.value_dim == self.head_dim else self.value_dim)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
+        n = self.names
         specs = {
-            "q_proj.weight": TensorSpec((self.q_width, self.hidden_size)),
-            "k_proj.weight": TensorSpec((self.kv_width, self.hidden_size)),
-            "v_proj.weight": TensorSpec((self.kv_width, self.hidden_size)),
-            "o_proj.weight": TensorSpec((self.hidden_size, self.q_width)),
+            n["q_proj.weight"]: TensorSpec((self.q_width, self.hidden_size)),
+            n["k_proj.weight"]: TensorSpec((self.kv_width, self.hidden_size)),
+            n["v_proj.weight"]: TensorSpec((self.v_width, self.hidden_size)),
+            n["o_proj.weight"]: TensorSpec((self.hidden_size, self.out_width)),
         }
         if self.qkv_bias:
-            specs["q_proj.bias"] = TensorSpec((self.q_width,), role="vector")
-            specs["k_proj.bias"] = TensorSpec((self.kv_width,), role="vector")
-            specs["v_proj.bias"] = TensorSpec((self.kv_width,), role="vector")
+            specs[n["q_proj.bias"]] = TensorSpec((self.q_width,), role="vector")
+            specs[n["k_proj.bias"]] = TensorSpec((self.kv_width,), role="vector")
+            specs[n["v_proj.bias"]] = TensorSpec((self.v_width,), role="vector")
+        if self.qk_norm:
+            specs[n["q_norm"]] = TensorSpec((self.q_width,), init="gain", role="vector")
+            specs[n["k_norm"]] = TensorSpec((self.kv_width,), init="gain", role="vector")
+        if self.distance_penalty:
+            specs[n["r1"]] = TensorSpec((self.num_heads,), init="gain", role="vector")
+            specs[n["r2"]] = TensorSpec((self.num_heads,), init="gain", role="vector")
         return specs
 
     def bind(self, tensors, runtime) -> None:
@@ -93,7 +145,7 @@ class Attention(Mixer):
             return rows.index_select(0, index.to(rows.device)).contiguous()
 
         def stacked(suffix):
-            q, k, v = (tensors[f"{name}_proj.{suffix}"] for name in "qkv")
+            q, k, v = (tensors[self.names[f"{name}_proj.{suffix}"]] for name in "qkv")
             if order is not None:
                 q, k = reorder(q, self.num_heads), reorder(k, self.num_kv_heads)
             if self.paired:
@@ -103,15 +155,41 @@ class Attention(Mixer):
 
         self.w_qkv = ops.prepare_weight(stacked("weight"))
         self.b_qkv = stacked("bias") if self.qkv_bias else None
-        self.w_o = runtime.ops.prepare_weight(tensors["o_proj.weight"])
+        self.w_o = runtime.ops.prepare_weight(tensors[self.names["o_proj.weight"]])
         if self.position is not None:
             self.position.bind({}, runtime)
-        runtime.ops.require_attention(self.head_dim)
+        self.q_gain = tensors[self.names["q_norm"]].contiguous() if self.qk_norm else None
+        self.k_gain = tensors[self.names["k_norm"]].contiguous() if self.qk_norm else None
+        self.distance = ((tensors[self.names["r1"]].contiguous(), tensors[self.names["r2"]].contiguous())
+                         if self.distance_penalty else None)
+        if not self.general:
+            runtime.ops.require_attention(self.head_dim)
 
     takes_normed_input = True   # x goes to ops.linear only
     kernels_through_ops = True  # every kernel of this part is a method of ``Ops``: a decode step may be recorded
 
+    def forward_general(self, x, ctx, binding):
+        """The layer with q/k norm, value norm, distance penalty or a value size of its own."""
+        import torch
+
+        rt = self.runtime
+        tokens = x.shape[0]
+        kv = binding.kv
+        qkv = rt.workspace.get("attention.qkv", tokens, self.qkv_width, rt.dtype)
+        qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, tag="attention.qkv", defer_bias=True)
+        q = rt.workspace.get("attention.q", tokens, self.q_width, rt.dtype)
+        rt.ops.norm_kv_write(qkv, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim,
+                             self.q_gain, self.k_gain, self.value_norm, self.norm_eps, q,
+                             write_cache=binding.owns_cache)
+        mixed = rt.workspace.get("attention.out", tokens, self.out_width, rt.dtype)
+        rt.ops.attention_generic(q, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,
+                                 self.scale, self.window, value_dim=self.value_dim, distance=self.distance)
+        update = rt.workspace.get("mixer.update32", tokens, self.hidden_size, torch.float32)
+        return rt.ops.linear(mixed, self.w_o, None, update)
+
     def forward(self, x, ctx, binding):
+        if self.general:
+            return self.forward_general(x, ctx, binding)
         rt = self.runtime
         tokens = x.shape[0]
         kv = binding.kv

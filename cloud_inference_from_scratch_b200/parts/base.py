@@ -2,7 +2,7 @@
 
 A part is built from constants only (its ``PartSpec.params``); it never sees a model
 configuration.  Each part says which tensors it needs (``tensor_specs``), takes them
-(``bind``) and runs on a flat batch of tokens (``forward``).  Five kinds exist:
+(``bind``) and runs on a flat batch of tokens (``forward``).  Six kinds exist:
 
 * ``Norm``              normalises the residual stream (after adding a pending update to it)
 * ``PositionEncoding``  owned by a mixer; gives the constants its kernels rotate with
@@ -10,6 +10,7 @@ configuration.  Each part says which tensors it needs (``tensor_specs``), takes 
                         a cache (``cache_spec``) and/or per-request state of fixed size
                         (``state_spec``)
 * ``FeedForward``       acts on each token alone
+* ``Connection``        how a sublayer reads several residual streams and writes them back
 * ``Block``             the arrangement of the above inside one layer
 
 Registering a new kind is ``register_part("mixer", "name", cls)``; a model description
@@ -36,7 +37,7 @@ class TensorSpec:
     """A tensor a part reads from the weight files.
 
     ``init`` is how the random-weights mode fills it: "normal" N(0, std), "gain"
-    1 + N(0, std), "zeros".  ``role`` "matrix" tensors are held in the compute dtype
+    1 + N(0, std), "eye" identity + N(0, std) (a square matrix), "zeros".  ``role`` "matrix" tensors are held in the compute dtype
     (bfloat16 unless the whole run is 32-bit); "vector" tensors (norm gains, biases)
     are held in float32, which keeps a 32-bit stored tensor as it is and widens a
     bfloat16 one without loss; "table" tensors are integer tables held as int32.
@@ -50,15 +51,23 @@ class TensorSpec:
 @dataclass(frozen=True)
 class CacheSpec:
     """What a mixer needs of the page manager: keys and values for ``kv_heads`` heads of
-    ``head_dim`` per token, for all earlier tokens (``window == 0``) or the last ``window``."""
+    ``head_dim`` per token, for all earlier tokens (``window == 0``) or the last ``window``.
+    ``value_dim`` is the size of a value head where it differs from that of a key head (0: the same)."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0
 
     @property
-    def group_key(self) -> tuple[int, int, int]:
-        return (self.window, self.kv_heads, self.head_dim)
+    def value_size(self) -> int:
+        return self.value_dim or self.head_dim
+
+    @property
+    def group_key(self) -> tuple[int, ...]:
+        if self.value_size == self.head_dim:
+            return (self.window, self.kv_heads, self.head_dim)
+        return (self.window, self.kv_heads, self.head_dim, self.value_size)
 
 
 @dataclass(frozen=True)
@@ -130,6 +139,20 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Connection(Part):
+    """How one sublayer meets ``streams`` side-by-side copies of the residual stream: the weights
+    it reads them with (``read_weights``: [streams] or None for a plain sum) and the not-yet-applied
+    write of its result (``pending(y)`` -> ``lazy.StreamUpdate``)."""
+
+    streams = 1
+
+    def read_weights(self) -> "torch.Tensor | None":
+        return None
+
+    def pending(self, y: "torch.Tensor") -> Any:
+        raise NotImplementedError
+
+
 class Block:
     """Arrangement of the parts of one layer around the residual stream.
 
@@ -168,7 +191,7 @@ class Block:
         return None
 
 
-_KINDS = ("norm", "position", "mixer", "feed_forward", "block")
+_KINDS = ("norm", "position", "mixer", "feed_forward", "connection", "block")
 _REGISTRY: dict[str, dict[str, type]] = {kind: {} for kind in _KINDS}
 
 

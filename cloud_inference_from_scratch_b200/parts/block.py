@@ -51,3 +51,31 @@ class PreNormResidual(Block):
 
 
 register_part("block", "prenorm_residual", PreNormResidual, replace=True)
+
+
+class StreamResidual(Block):
+    """Pre-norm layer over one residual stream or several: ``mixer`` and ``mixer_norm`` always,
+    ``feed_forward`` with ``feed_forward_norm`` if the layer has one, and per sublayer a
+    ``*_connection`` if the streams are read and written through hyper-connections (without one a
+    sublayer reads the sum of the streams and its result is added to each, which with one stream is
+    ``x + sublayer(norm(x))``).  Every write to the streams is left pending for the norm that reads
+    them next; the norms are ``StreamRMSNorm`` (they take ``read`` weights)."""
+
+    slots = ("mixer", "mixer_norm")
+
+    def forward(self, residual, pending, ctx, binding):
+        from ..lazy import StreamUpdate
+
+        for name in ("mixer", "feed_forward"):
+            part = self.parts.get(name)
+            if part is None:
+                continue
+            connection = self.parts.get(name + "_connection")
+            read = connection.read_weights() if connection is not None else None
+            x = self.parts[name + "_norm"].forward(residual, pending, ctx, read=read)
+            y = part.forward(x, ctx, binding) if name == "mixer" else part.forward(x, ctx)
+            pending = connection.pending(y) if connection is not None else StreamUpdate(y)
+        return pending
+
+
+register_part("block", "stream_residual", StreamResidual, replace=True)

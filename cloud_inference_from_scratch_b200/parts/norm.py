@@ -51,3 +51,38 @@ class RMSNorm(Norm):
 
 
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
+
+
+class StreamRMSNorm(Norm):
+    """RMS norm of what a sublayer reads from ``streams`` side-by-side copies of the residual
+    stream (``residual``: float32 [T, streams * H]; one stream is the ordinary case):
+    ``gain * u / sqrt(mean(u^2) + eps)`` with ``u = sum_t read[t] * stream_t``.  The gain is a
+    vector [H] or, with ``single_gain``, one number for all coordinates (stored as a tensor without
+    axes).  A pending ``StreamUpdate`` (or a plain tensor: the residual add) is applied to the
+    streams first, in the same kernel, in float32."""
+
+    def __init__(self, hidden_size: int, eps: float, single_gain: bool = False) -> None:
+        self.hidden_size = int(hidden_size)
+        self.eps = float(eps)
+        self.single_gain = bool(single_gain)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        if self.single_gain:
+            return {"": TensorSpec((), init="gain", role="vector")}
+        return {"weight": TensorSpec((self.hidden_size,), init="gain", role="vector")}
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        self.weight = tensors["" if self.single_gain else "weight"].reshape(-1).contiguous()
+
+    def forward(self, residual, update, ctx, rows=None, read=None):
+        rt = self.runtime
+        streams = residual.shape[1] // self.hidden_size
+        count = residual.shape[0] if rows is None else rows.shape[0]
+        out = rt.workspace.get("norm.out" if rows is None else "norm.rows", count,
+                               self.hidden_size, rt.dtype, per_request=rows is not None)
+        rt.ops.stream_norm(residual, streams, update, read, self.weight, self.eps, out, rows)
+        return out
+
+
+register_part("norm", "stream_rmsnorm", StreamRMSNorm, replace=True)

@@ -108,6 +108,8 @@ class RandomSource:
             values.normal_(0.0, self.std, generator=generator)
             if spec.init == "gain":
                 values += 1.0
+            elif spec.init == "eye":          # a square matrix near the identity
+                values += torch.eye(spec.shape[0], dtype=torch.float32, device=self.device)
             elif spec.init != "normal":
                 raise ValueError(f"tensor {name}: unknown init {spec.init!r}")
         for piece, factor in self.scales.items():
