@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl own|reference]
-                    [--config 3b|7b-mixed|14b-pressure] [--quick]
+                    [--config 3b|7b-mixed|14b-pressure|zisesun] [--quick]
 
 Prints ONE JSON line.  The default configuration is the Qwen2.5-3B shape: a "step" is one decode
 step of a batch of requests whose prompts (2,048 random tokens each) were prefilled before;
@@ -20,6 +20,12 @@ of 256 and 512 tokens, and (unless ``--quick``) the two other benchmark configur
   bf16 peak);
 * ``14b-pressure``: Qwen2.5-14B shape, 64 requests with prompts of 128 to 8,192 tokens on a cache
   pool half the size of their demand: generated tokens a second, preemptions, recomputed tokens.
+
+* ``zisesun``: the Zisesun design (windowed attention with q/k and value norms and a distance penalty,
+  lightning attention, routed experts, hyper-connections) at two sizes that resemble a real model's
+  layers, beside the Qwen2 dense shape of equal width, layer count, head sizes and active
+  feed-forward size: a 2,048-token prompt in one step, and decode steps of 8 requests at that
+  context, both through the step function.
 
 ``check`` compares, at the full 36 layers, the logits of the bfloat16 generation path with the
 32-bit path of the same weights (``engine/check.py``).  ``--config`` prints the line of one of the
@@ -554,6 +560,117 @@ def run_other_config(args: argparse.Namespace) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------- Zisesun beside Qwen2
+def _zisesun(width, layers, heads, kv_heads, dim, window, experts, top, ff, vocab=32000, streams=2) -> dict:
+    attention = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim,
+                                                  scale=dim ** -0.5, mask=dict(size=window)))
+    lightning = dict(type="lightning", mixer=dict(heads=heads, dim=dim, vdim=dim,
+                                                  decay=[1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)]))
+    mlp = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top))
+    return dict(architecture="Zisesun", vocab=vocab, width=width, max_positions=CONTEXT, norm=dict(eps=1e-6),
+                streams=streams, layers=[dict(attention if i % 2 == 0 else lightning, mlp=mlp) for i in range(layers)])
+
+
+# (Zisesun configuration, the Qwen2 dense shape of equal width, layers, heads and ACTIVE feed-forward size)
+ZISESUN_SIZES = {
+    "w2048": (_zisesun(2048, 8, 16, 2, 128, 1024, 16, 4, 1376), dict(_qwen2(2048, 8, 16, 2, 5504, 32000, False))),
+    "w4096": (_zisesun(4096, 4, 32, 8, 128, 1024, 32, 4, 2048), dict(_qwen2(4096, 4, 32, 8, 8192, 32000, False))),
+}
+
+
+def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int) -> dict:
+    """Prefill of one PROMPT_TOKENS prompt in one step (median of 5 after 3), then ``steps`` decode
+    steps of ``batch`` requests that each hold a PROMPT_TOKENS context, through the step function."""
+    import torch
+
+    from cloud_inference_from_scratch_b200 import models, parts  # noqa: F401
+    from cloud_inference_from_scratch_b200.engine.core import build_core
+    from cloud_inference_from_scratch_b200.engine.step import StepEntry
+
+    vocab = cfg.get("vocab", cfg.get("vocab_size"))
+    core = build_core(None, dtype="bfloat16", page_size=PAGE, num_pages=(batch + 1) * (CONTEXT // PAGE),
+                      max_requests=batch + 1, max_model_len=CONTEXT, max_tokens_per_step=PROMPT_TOKENS,
+                      random_config=cfg, seed=0, random_device="cuda")
+    ops = core.runtime.ops
+
+    def timed(fn) -> float:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop)
+
+    prompt = random_prompts(1, PROMPT_TOKENS, vocab, seed=99)[0]
+    times = []
+    launches = 0
+    for index in range(8):
+        core.step.admit("prefill")
+        before = ops.launches
+        with nvtx_range("bench.prefill"):
+            ms = timed(lambda: core.step.run([StepEntry("prefill", prompt, want=(PROMPT_TOKENS - 1,))]))
+        launches = ops.launches - before
+        core.step.release("prefill")
+        if index >= 3:
+            times.append(ms)
+    prefill_ms = statistics.median(times)
+    prompts = random_prompts(batch, PROMPT_TOKENS, vocab, seed=batch)
+    for index, tokens in enumerate(prompts):
+        core.step.admit(index)
+        core.step.run([StepEntry(index, tokens)])
+    token = [[int(t[0])] for t in prompts]
+    step = lambda: core.step.run([StepEntry(i, token[i], want=(0,)) for i in range(batch)])  # noqa: E731
+    for _ in range(warmup):
+        step()
+    before = ops.launches
+    with nvtx_range("bench.decode"):
+        decode_ms = timed(lambda: [step() for _ in range(steps)]) / steps
+    decode_launches = (ops.launches - before) // steps
+    ops.check_errors()
+    del core
+    torch.cuda.empty_cache()
+    return dict(prefill_ms=round(prefill_ms, 3), prefill_tokens_per_s=round(PROMPT_TOKENS / prefill_ms * 1e3, 1),
+                prefill_launches=launches, decode_ms_per_step=round(decode_ms, 4),
+                decode_tokens_per_s=round(batch / decode_ms * 1e3, 1), decode_launches=decode_launches)
+
+
+def run_zisesun(args: argparse.Namespace) -> int:
+    import torch
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device; this engine has no CPU path"}))
+        return 1
+    sampler = ClockSampler()
+    sampler.start()
+    points = {}
+    for name, (zisesun, qwen) in ZISESUN_SIZES.items():
+        if args.size not in ("all", name):
+            continue
+        if args.layers:
+            zisesun = dict(zisesun, layers=zisesun["layers"][:args.layers])
+            qwen = dict(qwen, num_hidden_layers=args.layers)
+        points[name] = {}
+        if args.model in ("both", "zisesun"):
+            points[name]["zisesun"] = _time_step_function(zisesun, args.batch, args.steps, args.warmup)
+        if args.model in ("both", "qwen2"):
+            points[name]["qwen2_dense"] = _time_step_function(qwen, args.batch, args.steps, args.warmup)
+        points[name]["layers"] = len(zisesun["layers"])
+    first = next(iter(points.values()))
+    main = first.get("zisesun") or first["qwen2_dense"]
+    line = {"metric": "decode tok/s, Zisesun design at width 2,048 (8 requests at context 2,048), step function",
+            "value": main["decode_tokens_per_s"], "unit": "tokens/s", "higher_is_better": True,
+            "ms_per_step": main["decode_ms_per_step"], "steps": args.steps, "n_gpus": 1, "warmup": args.warmup,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "own",
+            "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
+            "config": {"model": "Zisesun sizes beside Qwen2 dense shapes of equal width, layers, heads and active "
+                                "feed-forward size", "global_batch": args.batch, "seq_len": PROMPT_TOKENS,
+                       "page_size": PAGE, "parallelism": "single GPU", "inputs_larger_than_l2": True},
+            "points": points, "peaks": peaks(), "clocks": sampler.stop()}
+    print(json.dumps(without_nan(line)))
+    return 0
+
+
 def without_nan(value):
     """A part that was not measured (--only) is null in the record, not NaN."""
     if isinstance(value, dict):
@@ -586,7 +703,10 @@ def main() -> int:
                         help="prompt length of every request and of the timed prefill (the record's "
                              "default is 2048; longer ones are for profiles of long contexts, own arm only)")
     parser.add_argument("--impl", default="own", choices=("own", "reference"))
-    parser.add_argument("--config", default="3b", choices=("3b", "7b-mixed", "14b-pressure"),
+    parser.add_argument("--size", default="all", help="--config zisesun: one of its sizes (w2048, w4096)")
+    parser.add_argument("--model", default="both", choices=("both", "zisesun", "qwen2"),
+                        help="--config zisesun: only the new design, or only its dense peer")
+    parser.add_argument("--config", default="3b", choices=("3b", "7b-mixed", "14b-pressure", "zisesun"),
                         help="the benchmark configuration whose line is printed (default: the 3B line, "
                              "which also carries the other two as points)")
     parser.add_argument("--quick", action="store_true",
@@ -610,6 +730,8 @@ def main() -> int:
         CONTEXT = min(limit, PROMPT_TOKENS + max(2048, room))
     if args.impl == "reference":
         return run_reference(args)
+    if args.config == "zisesun":
+        return run_zisesun(args)
     if args.config != "3b":
         return run_other_config(args)
     return run_own(args)

@@ -57,6 +57,11 @@ struct PrefillArgs {
   float scale_log2;
   int window;
   int* err;
+  // a penalty that grows with the distance between query and key, per query head: the score (in
+  // units of log 2) is lowered by r1[h] * log2(1 + r2[h] * (position - key)); nullptr: none
+  const float* r1;
+  const float* r2;
+  int split_weights;   // the softmax weights enter the value product as two bfloat16 terms each
 };
 
 // One 64-key tile: thread t < 64 copies key row t of K, thread 64 + t row t of V, each with one bulk
@@ -125,11 +130,16 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
   // positions of the two rows this thread holds (-1: row not in use)
   const int g = lane >> 2, t4 = lane & 3;
   int row_pos[2];
+  float row_r1[2] = {0.f, 0.f}, row_r2[2] = {0.f, 0.f};
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + g + h * 8;
     const int tok = r / a.hpt, hh = h0 + r % a.hpt;
     row_pos[h] = (tok < ntok && hh < a.group) ? context + q0 + tok : -1;
+    if (a.r1 && row_pos[h] >= 0) {
+      row_r1[h] = a.r1[kvh * a.group + hh];
+      row_r2[h] = a.r2[kvh * a.group + hh];
+    }
   }
 
   bool alive = true;
@@ -172,11 +182,14 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
           const int key = k0 + i * 8 + 2 * t4 + (e & 1);
           const int pos = row_pos[e >> 1];
           const bool ok = key <= pos && (a.window <= 0 || key > pos - a.window);
-          s[i][e] = ok ? s[i][e] * a.scale_log2 : -INFINITY;
+          float score = s[i][e] * a.scale_log2;
+          if (a.r1 && ok) score -= row_r1[e >> 1] * __log2f(fmaf(row_r2[e >> 1], (float)(pos - key), 1.f));
+          s[i][e] = ok ? score : -INFINITY;
         }
       }
       softmax_update<BN / 8>(s, m, l, o);
-      accumulate<BN / 16>(s, v_s + stage * BN * ROW, o, lane);
+      if (a.split_weights) accumulate_split<BN / 16>(s, v_s + stage * BN * ROW, o, lane);
+      else accumulate<BN / 16>(s, v_s + stage * BN * ROW, o, lane);
     }
     __syncthreads();
   }
@@ -1121,14 +1134,18 @@ static const float kLog2e = 1.4426950408889634f;
 
 extern "C" int cie_attention_head_dim() { return D; }
 
-extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int out_stride,
-                                     const void* k_pool, const void* v_pool, const int* table,
-                                     int table_width, int num_pages, const int* tile_request,
-                                     const int* tile_q0, int num_tiles, const int* context_lens,
-                                     const int* query_lens, const int* query_start, int q_heads,
-                                     int kv_heads, int page_size, int hpt, float scale, int window,
-                                     int* err, void* stream) {
+// r1, r2: float32 [q_heads] of the distance penalty, or both null; split_weights: 1 keeps the
+// softmax weights to 16 bits of mantissa in the value product (two bfloat16 terms).
+extern "C" int cie_attention_prefill_ex(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* k_pool, const void* v_pool, const int* table,
+                                        int table_width, int num_pages, const int* tile_request,
+                                        const int* tile_q0, int num_tiles, const int* context_lens,
+                                        const int* query_lens, const int* query_start, int q_heads,
+                                        int kv_heads, int page_size, int hpt, float scale, int window,
+                                        const float* r1, const float* r2, int split_weights,
+                                        int* err, void* stream) {
   if (num_tiles <= 0) return 0;
+  if ((r1 == nullptr) != (r2 == nullptr)) CIE_FAIL("attention_prefill: the distance penalty needs both of its vectors");
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_prefill: %d query heads over %d kv heads", q_heads, kv_heads);
   const int group = q_heads / kv_heads;
   if (hpt < 1 || hpt > BM || hpt > group) CIE_FAIL("attention_prefill: %d heads per tile with a group of %d", hpt, group);
@@ -1140,6 +1157,7 @@ extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int
   a.query_lens = query_lens; a.query_start = query_start;
   a.group = group; a.hpt = hpt; a.tpt = BM / hpt; a.head_chunks = (group + hpt - 1) / hpt;
   a.scale_log2 = scale * kLog2e; a.window = window; a.err = err;
+  a.r1 = r1; a.r2 = r2; a.split_weights = split_weights;
   const size_t smem = (size_t)(BM + 4 * BN) * ROW * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
@@ -1150,6 +1168,19 @@ extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int
   dim3 grid(num_tiles, kv_heads * a.head_chunks);
   CIE_LAUNCH("attention_prefill", prefill_kernel, grid, dim3(PREFILL_WARPS * 32), smem, (cudaStream_t)stream, a);
   return 0;
+}
+
+extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int out_stride,
+                                     const void* k_pool, const void* v_pool, const int* table,
+                                     int table_width, int num_pages, const int* tile_request,
+                                     const int* tile_q0, int num_tiles, const int* context_lens,
+                                     const int* query_lens, const int* query_start, int q_heads,
+                                     int kv_heads, int page_size, int hpt, float scale, int window,
+                                     int* err, void* stream) {
+  return cie_attention_prefill_ex(q, q_stride, out, out_stride, k_pool, v_pool, table, table_width, num_pages,
+                                  tile_request, tile_q0, num_tiles, context_lens, query_lens, query_start,
+                                  q_heads, kv_heads, page_size, hpt, scale, window, nullptr, nullptr, 0, err,
+                                  stream);
 }
 
 // splits: CTAs that share the keys of one request (a thread-block cluster): 1, 2, 4 or 8.

@@ -163,6 +163,35 @@ __device__ __forceinline__ void accumulate(const float (&p)[NB * 2][4], const bf
   }
 }
 
+// The same with the weights kept to about 16 bits of mantissa: every float32 weight enters the
+// product as two bfloat16 terms, its rounding and the rounding of what that left over, so the
+// value product sees the weights to within 2^-17 of their size instead of 2^-9.
+template <int NB, bool SW = false>
+__device__ __forceinline__ void accumulate_split(const float (&p)[NB * 2][4], const bf16* v_tile,
+                                                 float (&o)[NTILES_D][4], int lane) {
+  const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kb = 0; kb < NB; ++kb) {
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const float p0 = p[2 * kb + (x >> 1)][2 * (x & 1)], p1 = p[2 * kb + (x >> 1)][2 * (x & 1) + 1];
+      const bf16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
+      hi[x] = pack_bf16(p0, p1);
+      lo[x] = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
+    }
+#pragma unroll
+    for (int db = 0; db < KSTEPS; ++db) {
+      uint32_t b[4];
+      ldsm_x4_trans(b, tile_ptr<SW>(v_tile, kb * 16 + (mi & 1) * 8 + r, db * 16 + (mi >> 1) * 8));
+      mma_bf16(o[2 * db], hi, b[0], b[1]);
+      mma_bf16(o[2 * db + 1], hi, b[2], b[3]);
+      mma_bf16(o[2 * db], lo, b[0], b[1]);
+      mma_bf16(o[2 * db + 1], lo, b[2], b[3]);
+    }
+  }
+}
+
 // Running-maximum softmax update for the two rows (g, g + 8) a thread holds.
 // s holds scores already multiplied by scale * log2(e); masked entries are -inf.
 // HALVES == 1: rows 8..15 of the block are not in use (at most 8 heads share a kv head) and are

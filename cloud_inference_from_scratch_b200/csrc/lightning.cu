@@ -91,6 +91,179 @@ lightning_scan_kernel(const T* __restrict__ proj, int proj_stride, float* __rest
   }
 }
 
+// ---------------------------------------------------------------- prompt portions in chunks
+// The same recurrence over chunks of up to kChunk tokens, so that a long portion is work for many
+// CTAs instead of one chain (all float32, CUDA cores; key and value sizes up to 128):
+//   1. per (chunk, head):    U = sum_j decay^(n-1-j) k_j v_j^T                       (n tokens in the chunk)
+//   2. per (request, head):  walks its chunks in order, S <- decay^n S + U, leaving in U's place the
+//                            state BEFORE the chunk; the last S goes back to the slot
+//   3. per (chunk, head):    o_i = decay^(i+1) S_before^T q_i + sum_{j<=i} decay^(i-j) (q_i.k_j) v_j
+// Chunks come as a work list (request, first token row, tokens) made on the host from the step's
+// portion lengths; a request's chunks follow each other.
+constexpr int kChunk = 32;
+constexpr int kChunkDim = 128;       // largest key and value size of the chunked kernels
+constexpr int kChunkRows = kChunkDim / kScanWarps;      // state rows of a warp
+constexpr int kChunkCols = kChunkDim / 32;              // value columns of a lane
+
+__device__ __forceinline__ float decay_power(float log2_decay, int n) { return n == 0 ? 1.f : exp2f(log2_decay * (float)n); }
+
+template <typename T>
+__global__ void __launch_bounds__(kScanWarps * 32)
+lightning_chunk_state_kernel(const T* __restrict__ proj, int proj_stride, float* __restrict__ chunk_state,
+                             const float* __restrict__ decay, const int* __restrict__ chunk_row,
+                             const int* __restrict__ chunk_count, int heads, int dim, int vdim) {
+  extern __shared__ float smem[];
+  float* k_s = smem;                          // [kChunk][dim], times decay^(n-1-j)
+  float* v_s = smem + kChunk * dim;           // [kChunk][vdim]
+  pdl_wait();
+  pdl_trigger();
+  const int chunk = blockIdx.x, head = blockIdx.y;
+  const int row0 = chunk_row[chunk], n = chunk_count[chunk];
+  const float log2_d = log2f(decay[head]);
+  const int k_off = heads * dim + head * dim, v_off = 2 * heads * dim + head * vdim;
+  for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
+    const int j = e / dim, i = e % dim;
+    k_s[e] = silu_f(to_float(proj[(size_t)(row0 + j) * proj_stride + k_off + i])) * decay_power(log2_d, n - 1 - j);
+  }
+  for (int e = threadIdx.x; e < n * vdim; e += blockDim.x) {
+    const int j = e / vdim, c = e % vdim;
+    v_s[e] = silu_f(to_float(proj[(size_t)(row0 + j) * proj_stride + v_off + c]));
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float u[kChunkRows][kChunkCols] = {};
+  for (int j = 0; j < n; ++j) {
+    float vv[kChunkCols];
+#pragma unroll
+    for (int c = 0; c < kChunkCols; ++c) vv[c] = lane + 32 * c < vdim ? v_s[j * vdim + lane + 32 * c] : 0.f;
+#pragma unroll
+    for (int r = 0; r < kChunkRows; ++r) {
+      const int i = warp + kScanWarps * r;
+      const float kv = i < dim ? k_s[j * dim + i] : 0.f;
+#pragma unroll
+      for (int c = 0; c < kChunkCols; ++c) u[r][c] = fmaf(kv, vv[c], u[r][c]);
+    }
+  }
+  float* dst = chunk_state + ((size_t)chunk * heads + head) * dim * vdim;
+#pragma unroll
+  for (int r = 0; r < kChunkRows; ++r) {
+    const int i = warp + kScanWarps * r;
+    if (i >= dim) continue;
+#pragma unroll
+    for (int c = 0; c < kChunkCols; ++c)
+      if (lane + 32 * c < vdim) dst[(size_t)i * vdim + lane + 32 * c] = u[r][c];
+  }
+}
+
+// grid: (requests, heads, blocks over dim * vdim)
+__global__ void lightning_chunk_prefix_kernel(float* __restrict__ chunk_state, float* __restrict__ state,
+                                              const float* __restrict__ decay,
+                                              const int* __restrict__ request_chunk_start,
+                                              const int* __restrict__ chunk_count, const int* __restrict__ slots,
+                                              const int* __restrict__ request_active, int heads, int dim, int vdim,
+                                              int max_slots, int* err) {
+  pdl_wait();
+  pdl_trigger();
+  const int request = blockIdx.x, head = blockIdx.y;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;
+  if (e >= dim * vdim) return;
+  const int slot = slots[request];
+  if (slot < 0 || slot >= max_slots) {
+    if (e == 0) atomicOr(err, kErrBadRequest);
+    return;
+  }
+  const float log2_d = log2f(decay[head]);
+  float* cell = state + ((size_t)slot * heads + head) * dim * vdim + e;
+  float s = *cell;
+  for (int chunk = request_chunk_start[request]; chunk < request_chunk_start[request + 1]; ++chunk) {
+    float* u = chunk_state + ((size_t)chunk * heads + head) * dim * vdim + e;
+    const float gained = *u;
+    *u = s;
+    s = fmaf(decay_power(log2_d, chunk_count[chunk]), s, gained);
+  }
+  if (request_active[request]) *cell = s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kScanWarps * 32)
+lightning_chunk_output_kernel(const T* __restrict__ proj, int proj_stride, float* __restrict__ out, int out_stride,
+                              const float* __restrict__ chunk_state, const float* __restrict__ decay,
+                              const int* __restrict__ chunk_row, const int* __restrict__ chunk_count, int heads,
+                              int dim, int vdim) {
+  extern __shared__ float smem[];
+  float* q_s = smem;                              // [kChunk][dim]
+  float* k_s = q_s + kChunk * dim;                // [kChunk][dim + 1]
+  float* v_s = k_s + kChunk * (dim + 1);          // [kChunk][vdim]
+  float* a_s = v_s + kChunk * vdim;               // [kChunk][kChunk]
+  pdl_wait();
+  pdl_trigger();
+  const int chunk = blockIdx.x, head = blockIdx.y;
+  const int row0 = chunk_row[chunk], n = chunk_count[chunk];
+  const float log2_d = log2f(decay[head]);
+  const int q_off = head * dim, k_off = heads * dim + head * dim, v_off = 2 * heads * dim + head * vdim;
+  for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
+    const int j = e / dim, i = e % dim;
+    const T* row = proj + (size_t)(row0 + j) * proj_stride;
+    q_s[j * dim + i] = silu_f(to_float(row[q_off + i]));
+    k_s[j * (dim + 1) + i] = silu_f(to_float(row[k_off + i]));
+  }
+  for (int e = threadIdx.x; e < n * vdim; e += blockDim.x) {
+    const int j = e / vdim, c = e % vdim;
+    v_s[e] = silu_f(to_float(proj[(size_t)(row0 + j) * proj_stride + v_off + c]));
+  }
+  __syncthreads();
+  // a[i][j] = decay^(i-j) q_i.k_j for j <= i (lanes run over j: k rows are padded by one element)
+  for (int e = threadIdx.x; e < n * kChunk; e += blockDim.x) {
+    const int i = e / kChunk, j = e % kChunk;
+    float dot = 0.f;
+    if (j <= i) {
+      for (int x = 0; x < dim; ++x) dot = fmaf(q_s[i * dim + x], k_s[j * (dim + 1) + x], dot);
+      dot *= decay_power(log2_d, i - j);
+    }
+    a_s[e] = dot;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* before = chunk_state + ((size_t)chunk * heads + head) * dim * vdim;
+  // a warp takes tokens warp, warp + 8, ...; a lane the value columns lane, lane + 32, ...
+  constexpr int kTokens = kChunk / kScanWarps;
+  float inter[kTokens][kChunkCols] = {}, intra[kTokens][kChunkCols] = {};
+  for (int x = 0; x < dim; ++x) {
+    float sv[kChunkCols];
+#pragma unroll
+    for (int c = 0; c < kChunkCols; ++c) sv[c] = lane + 32 * c < vdim ? before[(size_t)x * vdim + lane + 32 * c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t) {
+      const int i = warp + kScanWarps * t;
+      const float qv = i < n ? q_s[i * dim + x] : 0.f;
+#pragma unroll
+      for (int c = 0; c < kChunkCols; ++c) inter[t][c] = fmaf(qv, sv[c], inter[t][c]);
+    }
+  }
+  for (int j = 0; j < n; ++j) {
+    float vv[kChunkCols];
+#pragma unroll
+    for (int c = 0; c < kChunkCols; ++c) vv[c] = lane + 32 * c < vdim ? v_s[j * vdim + lane + 32 * c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t) {
+      const int i = warp + kScanWarps * t;
+      const float av = (i < n && j <= i) ? a_s[i * kChunk + j] : 0.f;
+#pragma unroll
+      for (int c = 0; c < kChunkCols; ++c) intra[t][c] = fmaf(av, vv[c], intra[t][c]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kTokens; ++t) {
+    const int i = warp + kScanWarps * t;
+    if (i >= n) continue;
+    const float carried = decay_power(log2_d, i + 1);
+#pragma unroll
+    for (int c = 0; c < kChunkCols; ++c)
+      if (lane + 32 * c < vdim)
+        out[(size_t)(row0 + i) * out_stride + head * vdim + lane + 32 * c] = fmaf(carried, inter[t][c], intra[t][c]);
+  }
+}
+
 // out[t][i] = gain[i] * o[t][i] * rsqrt(mean_i(o[t]^2) + eps) * sigmoid(gate[t][i]); one block per token.
 template <typename T>
 __global__ void lightning_gate_norm_kernel(const float* __restrict__ o, int o_stride, const T* __restrict__ gate,
@@ -136,6 +309,44 @@ extern "C" int cie_lightning_scan(const void* proj, int proj_stride, float* out,
   } else {
     CIE_FAIL("lightning_scan: unknown element type code %d", dtype);
   }
+  return 0;
+}
+
+extern "C" int cie_lightning_chunk_tokens() { return kChunk; }
+
+// The chunked form (see above).  chunk_state: float32 scratch [chunks][heads][dim][vdim].
+extern "C" int cie_lightning_chunked(const void* proj, int proj_stride, float* out, int out_stride, float* state,
+                                     float* chunk_state, const float* decay, const int* chunk_row,
+                                     const int* chunk_count, const int* request_chunk_start, const int* slots,
+                                     const int* request_active, int chunks, int requests, int heads, int dim,
+                                     int vdim, int max_slots, int dtype, int* err, void* stream) {
+  if (chunks <= 0 || requests <= 0) return 0;
+  if (dim < 1 || dim > kChunkDim || vdim < 1 || vdim > kChunkDim)
+    CIE_FAIL("lightning_chunked: key / value sizes %d / %d are outside 1..%d", dim, vdim, kChunkDim);
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem1 = (size_t)kChunk * (dim + vdim) * sizeof(float);
+  const size_t smem3 = (size_t)kChunk * (2 * dim + 1 + vdim + kChunk) * sizeof(float);
+  dim3 grid(chunks, heads), block(kScanWarps * 32);
+  dim3 grid2(requests, heads, (dim * vdim + 255) / 256);
+#define CIE_CHUNKED(T)                                                                                        \
+  do {                                                                                                        \
+    if (smem3 > 48 * 1024 &&                                                                                  \
+        cudaFuncSetAttribute(lightning_chunk_output_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                             (int)smem3) != cudaSuccess)                                                      \
+      CIE_FAIL("lightning_chunked: cannot reserve %zu bytes of shared memory", smem3);                        \
+    CIE_LAUNCH("lightning_chunk_state", lightning_chunk_state_kernel<T>, grid, block, smem1, s, (const T*)proj,  \
+               proj_stride, chunk_state, decay, chunk_row, chunk_count, heads, dim, vdim);                    \
+    CIE_LAUNCH("lightning_chunk_prefix", lightning_chunk_prefix_kernel, grid2, dim3(256), 0, s, chunk_state,   \
+               state, decay, request_chunk_start, chunk_count, slots, request_active, heads, dim, vdim,       \
+               max_slots, err);                                                                               \
+    CIE_LAUNCH("lightning_chunk_output", lightning_chunk_output_kernel<T>, grid, block, smem3, s,              \
+               (const T*)proj, proj_stride, out, out_stride, (const float*)chunk_state, decay, chunk_row,     \
+               chunk_count, heads, dim, vdim);                                                                \
+  } while (0)
+  if (dtype == kFloat32) CIE_CHUNKED(float);
+  else if (dtype == kBFloat16) CIE_CHUNKED(__nv_bfloat16);
+  else CIE_FAIL("lightning_chunked: unknown element type code %d", dtype);
+#undef CIE_CHUNKED
   return 0;
 }
 

@@ -209,6 +209,145 @@ moe_grouped_simt_kernel(const T* __restrict__ a, const T* __restrict__ w0, const
   }
 }
 
+// ---------------------------------------------------------------- grouped products (tensor cores)
+// bfloat16 operands, float32 accumulators, mma.sync m16n8k16.  A tile is 64 rows of one expert by
+// 64 output columns (gate_up: the 64 gate columns AND their 64 up columns, so that a thread ends
+// with both halves of SiLU(gate) * up); K advances in steps of 32 through a three-stage cp.async
+// ring.  Eight warps: two along the rows, four along the columns.  Rows are gathered by place;
+// rows and columns beyond the edges are zero-filled by the copy and never stored.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kTcStages = 3, kTcK = 32, kTcPad = 8, kTcCols = 64;
+
+template <bool kGateUp>
+__global__ void __launch_bounds__(256)
+moe_grouped_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w0,
+                      const __nv_bfloat16* __restrict__ w1, void* __restrict__ out,
+                      const int* __restrict__ place_to_pair, const int* __restrict__ tiles,
+                      const int* __restrict__ tile_count, int top, int n_total, int k_total) {
+  constexpr int kWRows = kGateUp ? 2 * kTcCols : kTcCols;
+  constexpr int kLd = kTcK + kTcPad;                      // 40 elements = 80 bytes a row
+  __shared__ __align__(16) __nv_bfloat16 a_s[kTcStages][kRowTile][kLd];
+  __shared__ __align__(16) __nv_bfloat16 w_s[kTcStages][kWRows][kLd];
+  __shared__ int src_row[kRowTile];
+  __shared__ int dst_row[kRowTile];
+  pdl_wait();
+  pdl_trigger();
+  if ((int)blockIdx.y >= tile_count[0]) return;
+  const int expert = tiles[3 * blockIdx.y], place0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < kRowTile) {
+    int src = -1, dst = -1;
+    if (tid < rows) {
+      const int pair = place_to_pair[place0 + tid];
+      src = kGateUp ? pair / top : place0 + tid;
+      dst = kGateUp ? place0 + tid : pair;
+    }
+    src_row[tid] = src;
+    dst_row[tid] = dst;
+  }
+  __syncthreads();
+  const int n0 = blockIdx.x * kTcCols;
+  const __nv_bfloat16* wg = w0 + (size_t)expert * n_total * k_total;
+  const __nv_bfloat16* wu = kGateUp ? w1 + (size_t)expert * n_total * k_total : nullptr;
+  const int k_steps = (k_total + kTcK - 1) / kTcK;
+
+  auto load_stage = [&](int stage, int step) {
+    const int k0 = step * kTcK;
+    {   // A: 64 rows x 4 chunks of 8 elements
+      const int r = tid >> 2, c = (tid & 3) * 8;
+      const int row = src_row[r];
+      const bool ok = row >= 0 && k0 + c < k_total;
+      cp_async16(&a_s[stage][r][c], ok ? a + (size_t)row * k_total + k0 + c : a, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < kWRows / 64; ++i) {
+      const int r = (tid >> 2) + i * 64, c = (tid & 3) * 8;
+      const bool up = kGateUp && r >= kTcCols;
+      const int gn = n0 + (up ? r - kTcCols : r);
+      const bool ok = gn < n_total && k0 + c < k_total;
+      const __nv_bfloat16* base = up ? wu : wg;
+      cp_async16(&w_s[stage][r][c], ok ? base + (size_t)gn * k_total + k0 + c : base, ok);
+    }
+  };
+
+  const int wm = warp >> 2, wn = warp & 3;        // rows 32 * wm .., columns 16 * wn .. (of gate and of up)
+  float acc[2][kGateUp ? 4 : 2][4] = {};
+#pragma unroll
+  for (int s = 0; s < kTcStages - 1; ++s) {
+    if (s < k_steps) load_stage(s, s);
+    cp_async_commit();
+  }
+  for (int step = 0; step < k_steps; ++step) {
+    cp_async_wait<kTcStages - 2>();
+    __syncthreads();
+    const int next = step + kTcStages - 1;
+    if (next < k_steps) load_stage(next % kTcStages, next);
+    cp_async_commit();
+    const int stage = step % kTcStages;
+#pragma unroll
+    for (int kk = 0; kk < kTcK; kk += 16) {
+      unsigned af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        ldmatrix_x4(af[mt], &a_s[stage][32 * wm + 16 * mt + (lane & 15)][kk + (lane >> 4) * 8]);
+      unsigned bf[kGateUp ? 2 : 1][4];
+      // two n-tiles of 8 columns a load: rows (lane & 7) + 8 * (lane >> 4), k half (lane >> 3) & 1
+      ldmatrix_x4(bf[0], &w_s[stage][16 * wn + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+      if constexpr (kGateUp)
+        ldmatrix_x4(bf[1], &w_s[stage][kTcCols + 16 * wn + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        mma_bf16(acc[mt][0], af[mt], bf[0][0], bf[0][1]);
+        mma_bf16(acc[mt][1], af[mt], bf[0][2], bf[0][3]);
+        if constexpr (kGateUp) {
+          mma_bf16(acc[mt][2], af[mt], bf[1][0], bf[1][1]);
+          mma_bf16(acc[mt][3], af[mt], bf[1][2], bf[1][3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = 32 * wm + 16 * mt + (lane >> 2) + 8 * half;
+      const int dst = dst_row[r];
+      if (dst < 0) continue;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int gn = n0 + 16 * wn + 8 * nt + (lane & 3) * 2 + e;
+          if (gn >= n_total) continue;
+          if constexpr (kGateUp) {
+            const float g = acc[mt][nt][2 * half + e], u = acc[mt][2 + nt][2 * half + e];
+            reinterpret_cast<__nv_bfloat16*>(out)[(size_t)dst * n_total + gn] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+          } else {
+            reinterpret_cast<float*>(out)[(size_t)dst * n_total + gn] = acc[mt][nt][2 * half + e];
+          }
+        }
+    }
+}
+
 // y[t][i] = sum_j weights[t][j] * rows[t * top + j][i], j ascending; float32 or activation type out.
 template <typename TOut>
 __global__ void moe_combine_kernel(const float* __restrict__ rows, const float* __restrict__ weights,
@@ -299,6 +438,34 @@ extern "C" int cie_moe_down_simt(const void* act, const void* w_down, float* row
   } else {
     CIE_FAIL("moe_down: unknown element type code %d", dtype);
   }
+  return 0;
+}
+
+// The same two products on the tensor cores: bfloat16 only, hidden and ff multiples of 8, pointers
+// aligned to 16 bytes (the caller checks).
+extern "C" int cie_moe_gate_up_tc(const void* x, const void* w_gate, const void* w_up, void* act,
+                                  const int* place_to_pair, const int* tiles, const int* tile_count,
+                                  int tokens, int top, int experts, int ff, int hidden, void* stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 8 || ff % 8) CIE_FAIL("moe_gate_up_tc: sizes %d / %d are no multiples of 8", hidden, ff);
+  const int max_tiles = (tokens * top + kRowTile - 1) / kRowTile + experts;
+  dim3 grid((ff + kTcCols - 1) / kTcCols, max_tiles);
+  CIE_LAUNCH("moe_gate_up_tc", moe_grouped_tc_kernel<true>, grid, dim3(256), 0, (cudaStream_t)stream,
+             (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, act, place_to_pair,
+             tiles, tile_count, top, ff, hidden);
+  return 0;
+}
+
+extern "C" int cie_moe_down_tc(const void* act, const void* w_down, float* rows, const int* place_to_pair,
+                               const int* tiles, const int* tile_count, int tokens, int top, int experts,
+                               int ff, int hidden, void* stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 8 || ff % 8) CIE_FAIL("moe_down_tc: sizes %d / %d are no multiples of 8", hidden, ff);
+  const int max_tiles = (tokens * top + kRowTile - 1) / kRowTile + experts;
+  dim3 grid((hidden + kTcCols - 1) / kTcCols, max_tiles);
+  CIE_LAUNCH("moe_down_tc", moe_grouped_tc_kernel<false>, grid, dim3(256), 0, (cudaStream_t)stream,
+             (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, (const __nv_bfloat16*)nullptr, (void*)rows,
+             place_to_pair, tiles, tile_count, top, hidden, ff);
   return 0;
 }
 

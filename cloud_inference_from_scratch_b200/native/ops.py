@@ -195,6 +195,26 @@ class Ops:
         """A matrix [N, K] as the matrix products want it: compute dtype, contiguous."""
         return weight.to(device=self.device, dtype=self.dtype).contiguous()
 
+    def attention_penalised(self, q: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
+                            head_dim: int, value_dim: int, scale: float, window: int, distance: Any) -> None:
+        """Attention with the options of ``attention_generic`` (a value size of its own, a distance
+        penalty), softmax weights float32 throughout.  bfloat16 prompt portions whose value heads have
+        the size of the key heads run on the tensor cores (mma.sync; the weights enter the value
+        product as two bfloat16 terms); single tokens, the 32-bit path and every other shape run on
+        the kernel that takes one warp per (token, head)."""
+        fast = self._tensor_attention.get(head_dim) if value_dim == head_dim and self.code == BF16 else None
+        singles = ctx.num_single
+        if (fast is None or singles == ctx.num_requests or q.shape[1] % 8 or out.shape[1] % 8
+                or os.environ.get("CIE_PENALISED_TC", "1") == "0"):
+            self.attention_generic(q, out, ctx, kv, q_heads, kv_heads, head_dim, scale, window,
+                                   value_dim=value_dim, distance=distance)
+            return
+        if singles:     # the leading rows of a mixed step are its single tokens
+            self.attention_generic(q[:singles], out[:singles], ctx, kv, q_heads, kv_heads, head_dim, scale,
+                                   window, value_dim=value_dim, distance=distance)
+        plan = ctx.extras.get(("attention", q_heads // kv_heads)) or None
+        fast.run_portions(q, out, ctx, kv, q_heads, kv_heads, scale, window, plan, distance, True)
+
     def require_attention(self, head_dim: int) -> None:
         """Builds, at model set-up, the attention kernels a head size needs."""
         if self.code == BF16:
@@ -343,7 +363,47 @@ class Ops:
             lib = _Lib(load_library("lightning.cu"))
             self._lightning_scan = lib.function("cie_lightning_scan", [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, v, v])
             self._lightning_gate_norm = lib.function("cie_lightning_gate_norm", [v, i, v, i, v, v, i, i, f, i, v])
+            self._lightning_chunked = lib.function(
+                "cie_lightning_chunked", [v, i, v, i, v, v, v, v, v, v, v, v, i, i, i, i, i, i, i, v, v])
+            self.lightning_chunk_tokens = int(lib.handle.cie_lightning_chunk_tokens())
             self._lightning_lib = lib
+
+    LIGHTNING_CHUNK_MAX_DIM = 128     # largest key and value size of the chunked kernels
+
+    def plan_lightning(self, host: Any) -> dict[str, Any]:
+        """Work lists of the chunked form for a step that holds prompt portions: every request's new
+        tokens cut into chunks (first token row and token count of each) and, per request, where its
+        chunks start.  A step of single tokens runs the recurrence directly and needs none."""
+        import numpy as np
+
+        if host.num_single == host.num_requests:
+            return {}
+        self._load_lightning()
+        size = self.lightning_chunk_tokens
+        rows, counts, starts = [], [], [0]
+        for first, length in zip(host.query_start[:-1].tolist(), host.query_lens.tolist()):
+            for offset in range(0, length, size):
+                rows.append(first + offset)
+                counts.append(min(size, length - offset))
+            starts.append(len(rows))
+        return {"chunk_row": np.asarray(rows, dtype=np.int32), "chunk_count": np.asarray(counts, dtype=np.int32),
+                "request_chunk_start": np.asarray(starts, dtype=np.int32)}
+
+    def lightning_chunked(self, proj: Any, out: Any, state: Any, decay: Any, ctx: Any, plan: dict[str, Any],
+                          heads: int, dim: int, vdim: int) -> None:
+        """The same recurrence as ``lightning_scan`` for a step with prompt portions, in chunks (see
+        ``plan_lightning``): chunk sums in parallel, a short walk over each request's chunks, outputs
+        in parallel.  Float32 throughout."""
+        self._flush()
+        self._load_lightning()
+        chunks = plan["chunk_row"].shape[0]
+        scratch = self.scratch("lightning.chunks", chunks * heads * dim * vdim)
+        self.launches += 3
+        self._lightning_chunked(_ptr(proj), proj.stride(0), _ptr(out), out.stride(0), _ptr(state), _ptr(scratch),
+                                _ptr(decay), _ptr(plan["chunk_row"]), _ptr(plan["chunk_count"]),
+                                _ptr(plan["request_chunk_start"]), _ptr(ctx.slots), _ptr(ctx.request_active),
+                                chunks, ctx.num_requests, heads, dim, vdim, state.shape[0], self._code_of(proj),
+                                _ptr(self.error_word), self.stream)
 
     def lightning_scan(self, proj: Any, out: Any, state: Any, decay: Any, ctx: Any, heads: int, dim: int,
                        vdim: int) -> None:
@@ -376,6 +436,8 @@ class Ops:
             self._moe_gate_up_simt = lib.function("cie_moe_gate_up_simt", [v, v, v, v, v, v, v, i, i, i, i, i, i, v])
             self._moe_down_simt = lib.function("cie_moe_down_simt", [v, v, v, v, v, v, i, i, i, i, i, i, v])
             self._moe_combine = lib.function("cie_moe_combine", [v, v, v, i, i, i, i, v])
+            self._moe_gate_up_tc = lib.function("cie_moe_gate_up_tc", [v, v, v, v, v, v, v, i, i, i, i, i, v])
+            self._moe_down_tc = lib.function("cie_moe_down_tc", [v, v, v, v, v, v, i, i, i, i, i, v])
             self.moe_row_tile = int(lib.handle.cie_moe_row_tile())
             self._moe_lib = lib
 
@@ -407,10 +469,18 @@ class Ops:
         self._moe_route(_ptr(x), _ptr(router), _ptr(correction), _ptr(ids), _ptr(weights), _ptr(counts),
                         _ptr(offsets), _ptr(cursors), _ptr(place_to_pair), _ptr(tiles), _ptr(tile_count), tokens,
                         hidden, experts, top, 1 if renormalize else 0, code, self.stream)
-        self._moe_gate_up_simt(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(act), _ptr(place_to_pair), _ptr(tiles),
-                               _ptr(tile_count), tokens, top, experts, ff, hidden, code, self.stream)
-        self._moe_down_simt(_ptr(act), _ptr(w_down), _ptr(rows), _ptr(place_to_pair), _ptr(tiles),
-                            _ptr(tile_count), tokens, top, experts, ff, hidden, code, self.stream)
+        if (code == BF16 and hidden % 8 == 0 and ff % 8 == 0 and os.environ.get("CIE_MOE_TC", "1") != "0"
+                and (x.data_ptr() | w_gate.data_ptr() | w_up.data_ptr() | w_down.data_ptr() | act.data_ptr()) % 16 == 0):
+            # bfloat16 on the tensor cores (mma.sync, float32 accumulators)
+            self._moe_gate_up_tc(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(act), _ptr(place_to_pair), _ptr(tiles),
+                                 _ptr(tile_count), tokens, top, experts, ff, hidden, self.stream)
+            self._moe_down_tc(_ptr(act), _ptr(w_down), _ptr(rows), _ptr(place_to_pair), _ptr(tiles),
+                              _ptr(tile_count), tokens, top, experts, ff, hidden, self.stream)
+        else:
+            self._moe_gate_up_simt(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(act), _ptr(place_to_pair), _ptr(tiles),
+                                   _ptr(tile_count), tokens, top, experts, ff, hidden, code, self.stream)
+            self._moe_down_simt(_ptr(act), _ptr(w_down), _ptr(rows), _ptr(place_to_pair), _ptr(tiles),
+                                _ptr(tile_count), tokens, top, experts, ff, hidden, code, self.stream)
         self._moe_combine(_ptr(rows), _ptr(weights), _ptr(out), tokens, hidden, top, self._code_of(out), self.stream)
         return out
 

@@ -90,6 +90,10 @@ class TensorAttention:
             "cie_attention_prefill",
             [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, i, v, v],
         )
+        self._prefill_ex = lib.function(
+            "cie_attention_prefill_ex",
+            [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, i, v, v, i, v, v],
+        )
         self._decode = lib.function(
             "cie_attention_decode",
             [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, i, i, v, v, f, i, i, v, v],
@@ -323,6 +327,30 @@ class TensorAttention:
                      ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, kv.page_size,
                      splits, chunks, MIN_KEYS_PER_CHUNKED_CTA, self._chunk_shares.data_ptr(), self._chunk_tickets.data_ptr(),
                      scale, window, self.use_tma, ops.error_word.data_ptr(), ops.stream)
+
+    def run_portions(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int, scale: float,
+                     window: int, plan: dict[str, Any] | None, distance: Any, split_weights: bool) -> None:
+        """The prompt portions of a step (every request after the leading single tokens) on the
+        mma.sync kernel, with the options the other kernels do not have: a distance penalty
+        (``distance``: float32 vectors r1, r2 per query head) and softmax weights that enter the value
+        product as two bfloat16 terms."""
+        ops = self.ops
+        torch = ops.torch
+        table = ctx.block_tables[kv.group]
+        group = q_heads // kv_heads
+        if plan is None:
+            tiles = plan_tiles(ctx.host.query_lens, group, skip=ctx.num_single)
+            plan = {name: torch.from_numpy(array).to(ops.device) for name, array in tiles.items()}
+        ops._flush()
+        ops.launches += 1
+        r1, r2 = distance if distance is not None else (None, None)
+        self._prefill_ex(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
+                         kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
+                         plan["tile_request"].data_ptr(), plan["tile_q0"].data_ptr(),
+                         plan["tile_request"].shape[0], ctx.context_lens.data_ptr(), ctx.query_lens.data_ptr(),
+                         ctx.query_start.data_ptr(), q_heads, kv_heads, kv.page_size, heads_per_tile(group),
+                         scale, window, None if r1 is None else r1.data_ptr(), None if r2 is None else r2.data_ptr(),
+                         1 if split_weights else 0, ops.error_word.data_ptr(), ops.stream)
 
     def run(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
             scale: float, window: int, plan: dict[str, Any] | None = None) -> bool:

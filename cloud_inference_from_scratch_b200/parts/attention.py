@@ -89,10 +89,11 @@ class Attention(Mixer):
                                            "q_proj.bias", "k_proj.bias", "v_proj.bias", "q_norm", "k_norm",
                                            "r1", "r2")}
         self.names.update(names or {})
+        self.tiled = False      # set at bind: whether prompt portions run on the tensor-core kernel
 
     @property
     def plan_key(self):
-        if self.general:      # its attention kernel walks the batch itself: no work lists
+        if self.general and not self.tiled:      # its attention kernel walks the batch itself: no work lists
             return None
         return ("attention", self.num_heads // self.num_kv_heads)
 
@@ -162,7 +163,10 @@ class Attention(Mixer):
         self.k_gain = tensors[self.names["k_norm"]].contiguous() if self.qk_norm else None
         self.distance = ((tensors[self.names["r1"]].contiguous(), tensors[self.names["r2"]].contiguous())
                          if self.distance_penalty else None)
-        if not self.general:
+        # the tensor-core kernels take bfloat16 heads of a multiple of 16 elements, values as large as keys
+        self.tiled = bool(self.value_dim == self.head_dim and self.head_dim % 16 == 0 and self.head_dim <= 256
+                          and runtime.dtype_name == "bfloat16")
+        if not self.general or self.tiled:
             runtime.ops.require_attention(self.head_dim)
 
     takes_normed_input = True   # x goes to ops.linear only
@@ -182,8 +186,8 @@ class Attention(Mixer):
                              self.q_gain, self.k_gain, self.value_norm, self.norm_eps, q,
                              write_cache=binding.owns_cache)
         mixed = rt.workspace.get("attention.out", tokens, self.out_width, rt.dtype)
-        rt.ops.attention_generic(q, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,
-                                 self.scale, self.window, value_dim=self.value_dim, distance=self.distance)
+        rt.ops.attention_penalised(q, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,
+                                   self.value_dim, self.scale, self.window, self.distance)
         update = rt.workspace.get("mixer.update32", tokens, self.hidden_size, torch.float32)
         return rt.ops.linear(mixed, self.w_o, None, update)
 

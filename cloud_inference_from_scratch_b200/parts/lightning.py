@@ -6,6 +6,10 @@ For input ``h``: ``q = silu(W_q h)``, ``k = silu(W_k h)`` (heads x dim), ``v = s
 request's state slot between steps.  The heads of ``o`` side by side are RMS-normalised together
 (gain vector ``norm``), multiplied by ``sigmoid(W_g h)`` and projected by ``W_o``.
 
+A step of single tokens runs the recurrence token by token; a step with prompt portions runs it in
+chunks of 32 tokens (chunk sums, a walk over each request's chunks, outputs), which is the same
+arithmetic in another order of additions, all float32.
+
 q, k, v and the gate come from ONE matrix product with the four weights stacked; the activation of
 q, k and v is applied in float32 inside the scan kernel, so that nothing that enters the recurrence
 is rounded after the projection.  The mixer holds no pages: its cache is the state alone.
@@ -33,6 +37,14 @@ class LightningAttention(Mixer):
         self.v_width = self.num_heads * self.value_dim
         self.names = dict(q="q", k="k", v="v", gate="g", out="o", norm="norm")
         self.names.update(names or {})
+
+    @property
+    def plan_key(self):
+        return ("lightning",)
+
+    def plan(self, host, cache):
+        """Chunk work lists for a step with prompt portions (one list serves every lightning layer)."""
+        return self.runtime.ops.plan_lightning(host)
 
     def state_spec(self) -> StateSpec:
         return StateSpec((self.num_heads, self.key_dim, self.value_dim), "float32")
@@ -67,8 +79,15 @@ class LightningAttention(Mixer):
         proj = rt.workspace.get("lightning.proj", tokens, width, rt.dtype)
         rt.ops.linear(x, self.w_in, None, proj)
         mixed = rt.workspace.get("lightning.o", tokens, self.v_width, torch.float32)
-        rt.ops.lightning_scan(proj, mixed, binding.state, self.decay_dev, ctx, self.num_heads,
-                              self.key_dim, self.value_dim)
+        plan = getattr(ctx, "extras", {}).get(self.plan_key) or None
+        limit = rt.ops.LIGHTNING_CHUNK_MAX_DIM
+        if plan and self.key_dim <= limit and self.value_dim <= limit:
+            # prompt portions: chunk sums, a short walk over the chunks, outputs, each wide
+            rt.ops.lightning_chunked(proj, mixed, binding.state, self.decay_dev, ctx, plan, self.num_heads,
+                                     self.key_dim, self.value_dim)
+        else:
+            rt.ops.lightning_scan(proj, mixed, binding.state, self.decay_dev, ctx, self.num_heads,
+                                  self.key_dim, self.value_dim)
         gated = rt.workspace.get("lightning.gated", tokens, self.v_width, rt.dtype)
         rt.ops.lightning_gate_norm(mixed, proj[:, 2 * self.qk_width + self.v_width:], self.gain, self.eps, gated)
         update = rt.workspace.get("mixer.update32", tokens, self.hidden_size, torch.float32)

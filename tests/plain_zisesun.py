@@ -8,8 +8,6 @@ as ``h @ W.T``; ``p`` maps a layer's tensor names (without the layer prefix) to 
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 F = torch.float64
@@ -35,25 +33,54 @@ def embedding(tokens: list[int], table: torch.Tensor, positions: torch.Tensor) -
     return table[ids] + positions[: len(tokens)]
 
 
+def lightning_recurrence(q, k, v, decay, state=None):
+    """q, k [T, heads, dim], v [T, heads, vdim] (after their activation); per head the state S
+    [dim, vdim] runs S <- decay * S + k v^T and o = S^T q.  Returns o [T, heads, vdim] and the
+    states after the last token [heads, dim, vdim]."""
+    tokens, heads, dim = q.shape
+    vdim = v.shape[-1]
+    out = torch.zeros(tokens, heads, vdim, dtype=F)
+    state = torch.zeros(heads, dim, vdim, dtype=F) if state is None else state.clone().to(F)
+    for head in range(heads):
+        for t in range(tokens):
+            state[head] = float(decay[head]) * state[head] + torch.outer(k[t, head], v[t, head])
+            out[t, head] = state[head].T @ q[t, head]
+    return out, state
+
+
 def lightning_mixer(h: torch.Tensor, p: dict, mixer: dict, eps: float) -> torch.Tensor:
-    """Linear attention with a fixed decay per head, run as the recurrence itself:
-    S <- decay * S + k v^T, o = S^T q; heads normalised together, gated, projected."""
+    """Linear attention with a fixed decay per head; heads normalised together, gated, projected."""
     heads, dim, vdim = mixer["heads"], mixer["dim"], mixer["vdim"]
     tokens = h.shape[0]
     q = silu(h @ p["mix.q"].T).view(tokens, heads, dim)
     k = silu(h @ p["mix.k"].T).view(tokens, heads, dim)
     v = silu(h @ p["mix.v"].T).view(tokens, heads, vdim)
-    out = torch.zeros(tokens, heads, vdim, dtype=F)
-    for head in range(heads):
-        decay = float(mixer["decay"][head])
-        state = torch.zeros(dim, vdim, dtype=F)
-        for t in range(tokens):
-            state = decay * state + torch.outer(k[t, head], v[t, head])
-            out[t, head] = state.T @ q[t, head]
+    out, _ = lightning_recurrence(q, k, v, mixer["decay"])
     flat = out.reshape(tokens, heads * vdim)
     flat = rms_divide(flat, eps) * p["mix.norm"]
     flat = flat * torch.sigmoid(h @ p["mix.g"].T)
     return flat @ p["mix.o"].T
+
+
+def windowed_softmax_attention(q, k, v, scale, window, r1, r2, first_position=0):
+    """q [T, heads, dim] at positions first_position.., k [N, groups, dim], v [N, groups, vdim] at
+    positions 0..N-1 (N = first_position + T).  Query head h reads group h // (heads / groups); query
+    position i sees keys j with 0 <= i - j < window (window 0: every j <= i); the score is
+    q.k * scale - r1_h * ln(1 + r2_h * (i - j)) (r1 None: no penalty); ordinary softmax."""
+    tokens, heads, _ = q.shape
+    groups = k.shape[1]
+    out = torch.zeros(tokens, heads, v.shape[-1], dtype=F)
+    for head in range(heads):
+        group = head // (heads // groups)
+        for t in range(tokens):
+            i = first_position + t
+            first = max(0, i - window + 1) if window else 0
+            keys = torch.arange(first, i + 1)
+            score = (k[keys, group] @ q[t, head]) * scale
+            if r1 is not None:
+                score = score - float(r1[head]) * torch.log1p(float(r2[head]) * (i - keys).to(F))
+            out[t, head] = torch.softmax(score, 0) @ v[keys, group]
+    return out
 
 
 def window_attention_mixer(h: torch.Tensor, p: dict, mixer: dict, eps: float) -> torch.Tensor:
@@ -69,17 +96,7 @@ def window_attention_mixer(h: torch.Tensor, p: dict, mixer: dict, eps: float) ->
     k = (rms_divide(k, eps) * p["mix.k.norm"]).view(tokens, groups, dim)
     v = rms_divide(v.view(tokens, groups, vdim), eps)
     window = (mixer.get("mask") or {}).get("size", 0)
-    out = torch.zeros(tokens, heads, vdim, dtype=F)
-    for head in range(heads):
-        group = head // (heads // groups)
-        r1, r2 = float(p["mix.r1"][head]), float(p["mix.r2"][head])
-        for i in range(tokens):
-            first = max(0, i - window + 1) if window else 0
-            keys = torch.arange(first, i + 1)
-            score = (k[keys, group] @ q[i, head]) * mixer["scale"]
-            score = score - r1 * torch.log1p(r2 * (i - keys).to(F))
-            weight = torch.softmax(score, 0)
-            out[i, head] = weight @ v[keys, group]
+    out = windowed_softmax_attention(q, k, v, mixer["scale"], window, p["mix.r1"], p["mix.r2"])
     return out.reshape(tokens, heads * vdim) @ p["mix.o"].T
 
 
@@ -128,7 +145,10 @@ def forward(config: dict, tensors: dict, tokens: list[int], keep_layers: bool = 
     streams = x.unsqueeze(0).repeat(streams_count or 1, 1, 1)
     kept = []
     for index, layer in enumerate(config["layers"]):
-        p = layer_tensors(tensors, layer.get("weights_of", index))
+        owner = index
+        while config["layers"][owner].get("weights_of") is not None:     # tensors of an earlier layer
+            owner = config["layers"][owner]["weights_of"]
+        p = layer_tensors(tensors, owner)
         mixer_fn = lambda h, layer=layer, p=p: run_mixer(layer["type"], h, p, layer["mixer"], eps)  # noqa: E731
         ff_fn = lambda h, layer=layer, p=p: routed_experts(h, p, layer["mlp"])  # noqa: E731
         if streams_count:
@@ -143,6 +163,17 @@ def forward(config: dict, tensors: dict, tokens: list[int], keep_layers: bool = 
     x = single_gain_norm(streams.sum(0), tensors["final.norm"].to(F), eps)
     logits = x @ tensors["head"].to(F).T
     return (logits, torch.stack(kept)) if keep_layers else logits
+
+
+def read_folder(folder):
+    """config.json and the tensors of a model folder."""
+    import json
+    from pathlib import Path
+
+    import safetensors.torch
+
+    config = json.loads((Path(folder) / "config.json").read_text())
+    return config, safetensors.torch.load_file(str(Path(folder) / "model.safetensors"))
 
 
 def greedy(config: dict, tensors: dict, prompt: list[int], count: int) -> list[int]:
