@@ -578,9 +578,11 @@ ZISESUN_SIZES = {
 }
 
 
-def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int) -> dict:
+def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int, only: str = "all") -> dict:
     """Prefill of one PROMPT_TOKENS prompt in one step (median of 5 after 3), then ``steps`` decode
-    steps of ``batch`` requests that each hold a PROMPT_TOKENS context, through the step function."""
+    steps of ``batch`` requests that each hold a PROMPT_TOKENS context, through the step function;
+    the decode steps replay the CUDA graph that the step function captures of a shape it has seen
+    three times, as the generation path does."""
     import torch
 
     from cloud_inference_from_scratch_b200 import models, parts  # noqa: F401
@@ -615,18 +617,26 @@ def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int) -> dict:
         if index >= 3:
             times.append(ms)
     prefill_ms = statistics.median(times)
+    if only == "prefill":
+        ops.check_errors()
+        return dict(prefill_ms=round(prefill_ms, 3), prefill_tokens_per_s=round(PROMPT_TOKENS / prefill_ms * 1e3, 1),
+                    prefill_launches=launches, decode_ms_per_step=float("nan"), decode_tokens_per_s=float("nan"))
     prompts = random_prompts(batch, PROMPT_TOKENS, vocab, seed=batch)
     for index, tokens in enumerate(prompts):
         core.step.admit(index)
         core.step.run([StepEntry(index, tokens)])
     token = [[int(t[0])] for t in prompts]
     step = lambda: core.step.run([StepEntry(i, token[i], want=(0,)) for i in range(batch)])  # noqa: E731
-    for _ in range(warmup):
-        step()
     before = ops.launches
+    step()
+    decode_launches = ops.launches - before          # kernels of one step, counted before it becomes a graph
+    core.step.enable_graphs(CONTEXT)
+    for _ in range(max(warmup, 4)):
+        step()
+    replays = core.step.graph_replays
     with nvtx_range("bench.decode"):
         decode_ms = timed(lambda: [step() for _ in range(steps)]) / steps
-    decode_launches = (ops.launches - before) // steps
+    assert core.step.graph_replays - replays == steps, "the decode steps did not run from the captured graph"
     ops.check_errors()
     del core
     torch.cuda.empty_cache()
@@ -652,9 +662,9 @@ def run_zisesun(args: argparse.Namespace) -> int:
             qwen = dict(qwen, num_hidden_layers=args.layers)
         points[name] = {}
         if args.model in ("both", "zisesun"):
-            points[name]["zisesun"] = _time_step_function(zisesun, args.batch, args.steps, args.warmup)
+            points[name]["zisesun"] = _time_step_function(zisesun, args.batch, args.steps, args.warmup, args.only)
         if args.model in ("both", "qwen2"):
-            points[name]["qwen2_dense"] = _time_step_function(qwen, args.batch, args.steps, args.warmup)
+            points[name]["qwen2_dense"] = _time_step_function(qwen, args.batch, args.steps, args.warmup, args.only)
         points[name]["layers"] = len(zisesun["layers"])
     first = next(iter(points.values()))
     main = first.get("zisesun") or first["qwen2_dense"]

@@ -111,6 +111,153 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   }
 }
 
+// ---------------------------------------------------------------- the heads of a group together
+// One CTA per (token, kv head, up to 8 query heads of its group): the heads share every key and value
+// row that is read.  Eight warps take blocks of 32 keys in turn; inside a block a lane owns one key
+// and reads its whole row with 16-byte loads (scores of all heads against it), then owns value
+// columns (lane, lane + 32, ...) while the block's keys go by.  Every warp keeps a running maximum,
+// sum and output of its own; they are joined in warp order at the end.  Same formula and options as
+// above; key sizes a multiple of the 16-byte vector up to 256, value sizes up to 128.
+constexpr int kGroupHeads = 8, kGroupWarps = 8, kGroupMaxV = 128;
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { static constexpr int n = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int n = 8; };
+
+template <typename T>
+__global__ void __launch_bounds__(kGroupWarps * 32)
+attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                       const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                       const int* __restrict__ positions, const int* __restrict__ request_of_token,
+                       const int* __restrict__ table, int table_width, int num_pages, int q_heads,
+                       int kv_heads, int dim, int vdim, int page_size, float scale, int window,
+                       const float* __restrict__ r1, const float* __restrict__ r2, int* err) {
+  constexpr int V = Vec16<T>::n;
+  extern __shared__ __align__(16) float group_smem[];
+  float* q_s = group_smem;                                   // [kGroupHeads][dim]
+  float* p_s = q_s + kGroupHeads * dim;                      // [warps][kGroupHeads][32]
+  float* o_s = p_s + kGroupWarps * kGroupHeads * 32;         // [warps][kGroupHeads][kGroupMaxV]
+  float* ml_s = o_s + kGroupWarps * kGroupHeads * kGroupMaxV;  // [warps][kGroupHeads][2]
+  long long* slot_s = reinterpret_cast<long long*>(ml_s + kGroupWarps * kGroupHeads * 2);   // [warps][32]
+  pdl_wait();
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x, kvh = blockIdx.y;
+  const int group = q_heads / kv_heads;
+  const int h0 = blockIdx.z * kGroupHeads, heads = min(kGroupHeads, group - h0);
+  const int pos = positions[t];
+  const int* row = table + (size_t)request_of_token[t] * table_width;
+  const int length = pos + 1;
+  const int first = (window > 0 && length > window) ? length - window : 0;
+  for (int e = threadIdx.x; e < kGroupHeads * dim; e += blockDim.x) {
+    const int h = e / dim, d = e % dim;
+    q_s[e] = h < heads ? to_float(q[(size_t)t * q_stride + (size_t)(kvh * group + h0 + h) * dim + d]) : 0.f;
+  }
+  float penalty[kGroupHeads], reach[kGroupHeads];
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) {
+    penalty[h] = (r1 && h < heads) ? r1[kvh * group + h0 + h] : 0.f;
+    reach[h] = (r1 && h < heads) ? r2[kvh * group + h0 + h] : 0.f;
+  }
+  __syncthreads();
+  float m[kGroupHeads], l[kGroupHeads], acc[kGroupHeads][kGroupMaxV / 32];
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) {
+    m[h] = -FLT_MAX;
+    l[h] = 0.f;
+#pragma unroll
+    for (int c = 0; c < kGroupMaxV / 32; ++c) acc[h][c] = 0.f;
+  }
+  float* my_p = p_s + warp * kGroupHeads * 32;
+  long long* my_slot = slot_s + warp * 32;
+  for (int base = first + warp * 32; base < length; base += kGroupWarps * 32) {
+    const int key = base + lane;
+    long long slot = -1;
+    if (key < length) {
+      const int index = key / page_size;
+      const int page = index < table_width ? row[index] : -1;
+      if (page < 0 || page >= num_pages) atomicOr(err, kErrBadPage);
+      else slot = ((long long)page * kv_heads + kvh) * page_size + key % page_size;
+    }
+    float dot[kGroupHeads];
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h) dot[h] = 0.f;
+    if (slot >= 0) {
+      const T* kr = k_pool + slot * dim;
+      for (int d0 = 0; d0 < dim; d0 += V) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(kr + d0);
+        const T* kv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int x = 0; x < V; ++x) {
+          const float kf = to_float(kv[x]);
+#pragma unroll
+          for (int h = 0; h < kGroupHeads; ++h) dot[h] = fmaf(q_s[h * dim + d0 + x], kf, dot[h]);
+        }
+      }
+    }
+    const float distance = (float)(pos - key);
+#pragma unroll
+    for (int h = 0; h < kGroupHeads; ++h) {
+      float s = -FLT_MAX;
+      if (slot >= 0) {
+        s = dot[h] * scale;
+        if (r1) s -= penalty[h] * log1pf(reach[h] * distance);
+      }
+      const float m_new = fmaxf(m[h], warp_max(s));
+      const float p = slot >= 0 ? expf(s - m_new) : 0.f;
+      const float alpha = expf(m[h] - m_new);
+      l[h] = l[h] * alpha + warp_sum(p);
+      m[h] = m_new;
+      my_p[h * 32 + lane] = p;
+#pragma unroll
+      for (int c = 0; c < kGroupMaxV / 32; ++c) acc[h][c] *= alpha;
+    }
+    my_slot[lane] = slot;
+    __syncwarp();
+    const int count = min(32, length - base);
+    for (int j = 0; j < count; ++j) {
+      const long long o = my_slot[j];
+      if (o < 0) continue;
+      const T* vr = v_pool + o * vdim;
+      float vv[kGroupMaxV / 32];
+#pragma unroll
+      for (int c = 0; c < kGroupMaxV / 32; ++c) vv[c] = lane + 32 * c < vdim ? to_float(vr[lane + 32 * c]) : 0.f;
+#pragma unroll
+      for (int h = 0; h < kGroupHeads; ++h) {
+        const float pj = my_p[h * 32 + j];
+#pragma unroll
+        for (int c = 0; c < kGroupMaxV / 32; ++c) acc[h][c] = fmaf(pj, vv[c], acc[h][c]);
+      }
+    }
+    __syncwarp();
+  }
+  // ---- join the warps, in warp order
+#pragma unroll
+  for (int h = 0; h < kGroupHeads; ++h) {
+#pragma unroll
+    for (int c = 0; c < kGroupMaxV / 32; ++c) o_s[(warp * kGroupHeads + h) * kGroupMaxV + lane + 32 * c] = acc[h][c];
+    if (lane == 0) {
+      ml_s[(warp * kGroupHeads + h) * 2] = m[h];
+      ml_s[(warp * kGroupHeads + h) * 2 + 1] = l[h];
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
+    const int h = e / vdim, d = e % vdim;
+    float top = -FLT_MAX;
+#pragma unroll
+    for (int w = 0; w < kGroupWarps; ++w) top = fmaxf(top, ml_s[(w * kGroupHeads + h) * 2]);
+    float sum = 0.f, value = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGroupWarps; ++w) {
+      const float share = expf(ml_s[(w * kGroupHeads + h) * 2] - top);
+      sum = fmaf(share, ml_s[(w * kGroupHeads + h) * 2 + 1], sum);
+      value = fmaf(share, o_s[(w * kGroupHeads + h) * kGroupMaxV + d], value);
+    }
+    out[(size_t)t * out_stride + (size_t)(kvh * group + h0 + h) * vdim + d] = from_float<T>(sum > 0.f ? value / sum : 0.f);
+  }
+}
+
 }  // namespace cie
 
 using namespace cie;
@@ -133,6 +280,32 @@ extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, 
   const long long items = (long long)tokens * q_heads;
   const int blocks = (int)((items + kWarps - 1) / kWarps);
   cudaStream_t s = (cudaStream_t)stream;
+  // the kernel that shares the keys among the heads of a group, where the sizes allow its 16-byte loads
+  const int vec = dtype == kFloat32 ? 4 : 8;
+  static const bool grouped = [] { const char* v = getenv("CIE_ATTENTION_GROUPED"); return !(v && v[0] == '0'); }();
+  if (grouped && dim % vec == 0 && vdim <= kGroupMaxV && (dtype == kFloat32 || dtype == kBFloat16) &&
+      (reinterpret_cast<uintptr_t>(k_pool) & 15) == 0) {
+    const int group = q_heads / kv_heads;
+    const size_t smem = sizeof(float) * ((size_t)kGroupHeads * dim + kGroupWarps * kGroupHeads * (32 + kGroupMaxV + 2)) +
+                        sizeof(long long) * kGroupWarps * 32;
+    dim3 grid(tokens, kv_heads, (group + kGroupHeads - 1) / kGroupHeads);
+    if (dtype == kFloat32) {
+      if (cudaFuncSetAttribute(attention_group_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        CIE_FAIL("attention_generic: cannot reserve %zu bytes of shared memory", smem);
+      CIE_LAUNCH("attention_group", attention_group_kernel<float>, grid, dim3(kGroupWarps * 32), smem, s,
+          (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool, positions,
+          request_of_token, table, table_width, num_pages, q_heads, kv_heads, dim, vdim, page_size, scale, window,
+          r1, r2, err);
+    } else {
+      if (cudaFuncSetAttribute(attention_group_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        CIE_FAIL("attention_generic: cannot reserve %zu bytes of shared memory", smem);
+      CIE_LAUNCH("attention_group", attention_group_kernel<__nv_bfloat16>, grid, dim3(kGroupWarps * 32), smem, s,
+          (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
+          (const __nv_bfloat16*)v_pool, positions, request_of_token, table, table_width, num_pages, q_heads,
+          kv_heads, dim, vdim, page_size, scale, window, r1, r2, err);
+    }
+    return 0;
+  }
   if (dtype == kFloat32) {
     CIE_LAUNCH("attention_generic", attention_generic_kernel<float>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,

@@ -175,11 +175,27 @@ __global__ void lightning_chunk_prefix_kernel(float* __restrict__ chunk_state, f
   const float log2_d = log2f(decay[head]);
   float* cell = state + ((size_t)slot * heads + head) * dim * vdim + e;
   float s = *cell;
-  for (int chunk = request_chunk_start[request]; chunk < request_chunk_start[request + 1]; ++chunk) {
+  const size_t stride = (size_t)heads * dim * vdim;
+  const int last = request_chunk_start[request + 1];
+  // eight chunks at a time: their sums are asked for together, before the first store, so that the
+  // walk waits for memory once per eight chunks and not once per chunk
+  constexpr int kBatch = 8;
+  for (int chunk = request_chunk_start[request]; chunk < last; chunk += kBatch) {
     float* u = chunk_state + ((size_t)chunk * heads + head) * dim * vdim + e;
-    const float gained = *u;
-    *u = s;
-    s = fmaf(decay_power(log2_d, chunk_count[chunk]), s, gained);
+    float gained[kBatch], power[kBatch];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const bool in = chunk + b < last;
+      gained[b] = in ? u[b * stride] : 0.f;
+      power[b] = in ? decay_power(log2_d, chunk_count[chunk + b]) : 1.f;
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      if (chunk + b < last) {
+        u[b * stride] = s;
+        s = fmaf(power[b], s, gained[b]);
+      }
+    }
   }
   if (request_active[request]) *cell = s;
 }

@@ -4,7 +4,7 @@
 //              over all experts (softmax), the `top` largest of score + correction, and as mixing
 //              weights the scores of the chosen experts (optionally renormalised to sum 1)
 //   plan       counts per expert -> offsets; every (token, choice) pair gets a place in its expert's
-//              run of rows; runs are cut into tiles of 64 rows for the grouped products
+//              run of rows; runs are cut into tiles of 128 rows for the grouped products
 //   gate_up    rows gathered by place, times the expert's stacked gate and up matrices, SiLU(gate)*up
 //   down       times the expert's down matrix, written to the pair's own row (float32)
 //   combine    y[t] = sum over the token's choices, in the order they were chosen, of weight * row
@@ -21,31 +21,52 @@ CIE_DEFINE_LAST_ERROR()
 namespace cie {
 
 constexpr int kMaxExperts = 1024;
-constexpr int kRowTile = 64;          // rows of a tile of the grouped products
+constexpr int kRowTile = 128;         // rows of a tile of the grouped products
 
 // ---------------------------------------------------------------- route
-// One warp per token.  ids / weights: [tokens][top]; counts[e] += 1 per choice.
+// One block of four warps per token: the token's row goes to shared memory as float32, the warps
+// share the experts (a lane strides over the row with 16-byte loads of the router matrix where the
+// row length allows), then the first warp turns logits into scores and chooses.
+// ids / weights: [tokens][top]; counts[e] += 1 per choice.
+constexpr int kRouteWarps = 4;
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router,
-                                 const float* __restrict__ correction, int* __restrict__ ids,
-                                 float* __restrict__ weights, int* __restrict__ counts, int tokens,
-                                 int hidden, int experts, int top, int renormalize) {
-  extern __shared__ float score_s[];      // [warps][2 * experts]: scores, then choice scores
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router,
+                 const float* __restrict__ correction, int* __restrict__ ids,
+                 float* __restrict__ weights, int* __restrict__ counts, int tokens,
+                 int hidden, int experts, int top, int renormalize) {
+  extern __shared__ __align__(16) float score_s[];      // [2 * experts]: scores, then choice scores; then the row
   pdl_wait();
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= tokens) return;
-  float* score = score_s + (size_t)warp * 2 * experts;
+  const int t = blockIdx.x;
+  float* score = score_s;
   float* choice = score + experts;
+  float* row_s = score_s + ((2 * experts + 3) & ~3);
   const T* row = x + (size_t)t * hidden;
-  for (int e = 0; e < experts; ++e) {
+  for (int k = threadIdx.x; k < hidden; k += blockDim.x) row_s[k] = to_float(row[k]);
+  __syncthreads();
+  const bool wide = hidden % 4 == 0;
+  for (int e = warp; e < experts; e += kRouteWarps) {
     const float* w = router + (size_t)e * hidden;
     float dot = 0.f;
-    for (int k = lane; k < hidden; k += 32) dot = fmaf(to_float(row[k]), w[k], dot);
+    if (wide) {
+      for (int k = 4 * lane; k < hidden; k += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + k);
+        const float4 xv = *reinterpret_cast<const float4*>(row_s + k);
+        dot = fmaf(xv.x, wv.x, dot);
+        dot = fmaf(xv.y, wv.y, dot);
+        dot = fmaf(xv.z, wv.z, dot);
+        dot = fmaf(xv.w, wv.w, dot);
+      }
+    } else {
+      for (int k = lane; k < hidden; k += 32) dot = fmaf(row_s[k], w[k], dot);
+    }
     dot = warp_sum(dot);
     if (lane == 0) score[e] = dot;
   }
+  __syncthreads();
+  if (warp != 0) return;
   __syncwarp();
   float m = -FLT_MAX;
   for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[e]);
@@ -127,7 +148,8 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, const int* __restri
 }
 
 // ---------------------------------------------------------------- grouped products (CUDA cores)
-// Tile y of the grid is tile y of the plan (blocks beyond tile_count leave at once).
+// Block y of the grid takes half (64 rows) of tile y / 2 of the plan (blocks beyond tile_count leave
+// at once).
 //   kGateUp  A row p = x[place_to_pair[p] / top]; W = w_gate[e], w_up[e] ([ff][hidden] each);
 //            out[p][n] = SiLU(a.gate_n) * (a.up_n), activation type, rows by place
 //   else     A row p = act[p]; W = w_down[e] ([hidden][ff]); out[place_to_pair[p]][n], float32
@@ -137,16 +159,19 @@ moe_grouped_simt_kernel(const T* __restrict__ a, const T* __restrict__ w0, const
                         void* __restrict__ out, const int* __restrict__ place_to_pair,
                         const int* __restrict__ tiles, const int* __restrict__ tile_count, int top,
                         int n_total, int k_total) {
-  constexpr int kTileN = 64, kTileK = 16;
-  __shared__ float a_tile[kTileK][kRowTile + 4];
+  constexpr int kTileN = 64, kTileK = 16, kHalf = 64;
+  static_assert(kRowTile == 2 * kHalf, "a block takes half a tile");
+  __shared__ float a_tile[kTileK][kHalf + 4];
   __shared__ float w_tile[kGateUp ? 2 : 1][kTileK][kTileN + 4];
-  __shared__ int src_row[kRowTile];
+  __shared__ int src_row[kHalf];
   pdl_wait();
   pdl_trigger();
-  if ((int)blockIdx.y >= tile_count[0]) return;
-  const int expert = tiles[3 * blockIdx.y], place0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+  const int tile = blockIdx.y >> 1, half = blockIdx.y & 1;
+  if (tile >= tile_count[0]) return;
+  const int expert = tiles[3 * tile], place0 = tiles[3 * tile + 1] + kHalf * half, rows = tiles[3 * tile + 2] - kHalf * half;
+  if (rows <= 0) return;
   const int tid = threadIdx.x;
-  if (tid < kRowTile) {
+  if (tid < kHalf) {
     int r = -1;
     if (tid < rows) r = kGateUp ? place_to_pair[place0 + tid] / top : place0 + tid;
     src_row[tid] = r;
@@ -210,10 +235,10 @@ moe_grouped_simt_kernel(const T* __restrict__ a, const T* __restrict__ w0, const
 }
 
 // ---------------------------------------------------------------- grouped products (tensor cores)
-// bfloat16 operands, float32 accumulators, mma.sync m16n8k16.  A tile is 64 rows of one expert by
+// bfloat16 operands, float32 accumulators, mma.sync m16n8k16.  A tile is 128 rows of one expert by
 // 64 output columns (gate_up: the 64 gate columns AND their 64 up columns, so that a thread ends
-// with both halves of SiLU(gate) * up); K advances in steps of 32 through a three-stage cp.async
-// ring.  Eight warps: two along the rows, four along the columns.  Rows are gathered by place;
+// with both halves of SiLU(gate) * up); K advances in steps of 32 through a four-stage cp.async
+// ring.  Eight warps: four along the rows, two along the columns.  Rows are gathered by place;
 // rows and columns beyond the edges are zero-filled by the copy and never stored.
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -234,18 +259,28 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-constexpr int kTcStages = 3, kTcK = 32, kTcPad = 8, kTcCols = 64;
+constexpr int kTcStages = 4, kTcK = 32, kTcPad = 8, kTcCols = 64;
+constexpr int kTcLd = kTcK + kTcPad;                      // 40 elements = 80 bytes a row: ldmatrix without conflicts
+
+template <bool kGateUp>
+constexpr size_t moe_tc_smem() {
+  return (size_t)kTcStages * (kRowTile + (kGateUp ? 2 : 1) * kTcCols) * kTcLd * sizeof(__nv_bfloat16);
+}
 
 template <bool kGateUp>
 __global__ void __launch_bounds__(256)
 moe_grouped_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w0,
                       const __nv_bfloat16* __restrict__ w1, void* __restrict__ out,
                       const int* __restrict__ place_to_pair, const int* __restrict__ tiles,
-                      const int* __restrict__ tile_count, int top, int n_total, int k_total) {
+                      const int* __restrict__ tile_count, int top, int n_total, int k_total, int interleaved) {
+  // interleaved (gate_up only): w0 holds [experts][2 * n_total][k], 16 gate rows, their 16 up rows, ...
   constexpr int kWRows = kGateUp ? 2 * kTcCols : kTcCols;
-  constexpr int kLd = kTcK + kTcPad;                      // 40 elements = 80 bytes a row
-  __shared__ __align__(16) __nv_bfloat16 a_s[kTcStages][kRowTile][kLd];
-  __shared__ __align__(16) __nv_bfloat16 w_s[kTcStages][kWRows][kLd];
+  constexpr int kNT = kGateUp ? 8 : 4;                    // 8-column accumulators of a warp
+  extern __shared__ __align__(16) unsigned char tc_smem[];
+  typedef __nv_bfloat16 (*ATile)[kRowTile][kTcLd];
+  typedef __nv_bfloat16 (*WTile)[kWRows][kTcLd];
+  ATile a_s = reinterpret_cast<ATile>(tc_smem);
+  WTile w_s = reinterpret_cast<WTile>(tc_smem + (size_t)kTcStages * kRowTile * kTcLd * sizeof(__nv_bfloat16));
   __shared__ int src_row[kRowTile];
   __shared__ int dst_row[kRowTile];
   pdl_wait();
@@ -265,31 +300,34 @@ moe_grouped_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
   }
   __syncthreads();
   const int n0 = blockIdx.x * kTcCols;
-  const __nv_bfloat16* wg = w0 + (size_t)expert * n_total * k_total;
-  const __nv_bfloat16* wu = kGateUp ? w1 + (size_t)expert * n_total * k_total : nullptr;
+  const __nv_bfloat16* wg = w0 + (size_t)expert * (interleaved ? 2 : 1) * n_total * k_total;
+  const __nv_bfloat16* wu = (kGateUp && !interleaved) ? w1 + (size_t)expert * n_total * k_total : nullptr;
   const int k_steps = (k_total + kTcK - 1) / kTcK;
 
   auto load_stage = [&](int stage, int step) {
     const int k0 = step * kTcK;
-    {   // A: 64 rows x 4 chunks of 8 elements
-      const int r = tid >> 2, c = (tid & 3) * 8;
+    const int c = (tid & 3) * 8;
+#pragma unroll
+    for (int i = 0; i < kRowTile / 64; ++i) {       // A: 128 rows x 4 pieces of 8 elements
+      const int r = (tid >> 2) + i * 64;
       const int row = src_row[r];
       const bool ok = row >= 0 && k0 + c < k_total;
       cp_async16(&a_s[stage][r][c], ok ? a + (size_t)row * k_total + k0 + c : a, ok);
     }
 #pragma unroll
     for (int i = 0; i < kWRows / 64; ++i) {
-      const int r = (tid >> 2) + i * 64, c = (tid & 3) * 8;
+      const int r = (tid >> 2) + i * 64;
       const bool up = kGateUp && r >= kTcCols;
       const int gn = n0 + (up ? r - kTcCols : r);
       const bool ok = gn < n_total && k0 + c < k_total;
-      const __nv_bfloat16* base = up ? wu : wg;
-      cp_async16(&w_s[stage][r][c], ok ? base + (size_t)gn * k_total + k0 + c : base, ok);
+      const __nv_bfloat16* base = (up && !interleaved) ? wu : wg;
+      const size_t w_row = interleaved ? (size_t)(gn >> 4) * 32 + (gn & 15) + (up ? 16 : 0) : (size_t)gn;
+      cp_async16(&w_s[stage][r][c], ok ? base + w_row * k_total + k0 + c : wg, ok);
     }
   };
 
-  const int wm = warp >> 2, wn = warp & 3;        // rows 32 * wm .., columns 16 * wn .. (of gate and of up)
-  float acc[2][kGateUp ? 4 : 2][4] = {};
+  const int wm = warp >> 1, wn = warp & 1;        // rows 32 * wm .., columns 32 * wn .. (of gate and of up)
+  float acc[2][kNT][4] = {};
 #pragma unroll
   for (int s = 0; s < kTcStages - 1; ++s) {
     if (s < k_steps) load_stage(s, s);
@@ -308,18 +346,16 @@ moe_grouped_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt)
         ldmatrix_x4(af[mt], &a_s[stage][32 * wm + 16 * mt + (lane & 15)][kk + (lane >> 4) * 8]);
-      unsigned bf[kGateUp ? 2 : 1][4];
-      // two n-tiles of 8 columns a load: rows (lane & 7) + 8 * (lane >> 4), k half (lane >> 3) & 1
-      ldmatrix_x4(bf[0], &w_s[stage][16 * wn + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
-      if constexpr (kGateUp)
-        ldmatrix_x4(bf[1], &w_s[stage][kTcCols + 16 * wn + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+      // a load gives two accumulators' worth (16 columns): rows (lane & 7) + 8 * (lane >> 4), k half (lane >> 3) & 1
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        mma_bf16(acc[mt][0], af[mt], bf[0][0], bf[0][1]);
-        mma_bf16(acc[mt][1], af[mt], bf[0][2], bf[0][3]);
-        if constexpr (kGateUp) {
-          mma_bf16(acc[mt][2], af[mt], bf[1][0], bf[1][1]);
-          mma_bf16(acc[mt][3], af[mt], bf[1][2], bf[1][3]);
+      for (int nb = 0; nb < kNT / 2; ++nb) {
+        const int w_row = (nb >= 2 ? kTcCols + 16 * (nb - 2) : 16 * nb) + 32 * wn;
+        unsigned bf[4];
+        ldmatrix_x4(bf, &w_s[stage][w_row + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma_bf16(acc[mt][2 * nb], af[mt], bf[0], bf[1]);
+          mma_bf16(acc[mt][2 * nb + 1], af[mt], bf[2], bf[3]);
         }
       }
     }
@@ -333,13 +369,13 @@ moe_grouped_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
       const int dst = dst_row[r];
       if (dst < 0) continue;
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int gn = n0 + 16 * wn + 8 * nt + (lane & 3) * 2 + e;
+          const int gn = n0 + 32 * wn + 8 * nt + (lane & 3) * 2 + e;
           if (gn >= n_total) continue;
           if constexpr (kGateUp) {
-            const float g = acc[mt][nt][2 * half + e], u = acc[mt][2 + nt][2 * half + e];
+            const float g = acc[mt][nt][2 * half + e], u = acc[mt][4 + nt][2 * half + e];
             reinterpret_cast<__nv_bfloat16*>(out)[(size_t)dst * n_total + gn] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
           } else {
             reinterpret_cast<float*>(out)[(size_t)dst * n_total + gn] = acc[mt][nt][2 * half + e];
@@ -380,13 +416,18 @@ extern "C" int cie_moe_route(const void* x, const float* router, const float* co
   if (top < 1 || top > experts || top > 32) CIE_FAIL("moe_route: top %d of %d experts (at most 32)", top, experts);
   cudaStream_t s = (cudaStream_t)stream;
   if (cudaMemsetAsync(counts, 0, sizeof(int) * experts, s) != cudaSuccess) CIE_FAIL("moe_route: memset failed");
-  const int warps = 4;
-  const size_t smem = (size_t)warps * 2 * experts * sizeof(float);
-  const int blocks = (tokens + warps - 1) / warps;
+  const int warps = kRouteWarps;
+  const size_t smem = (size_t)(((2 * experts + 3) & ~3) + hidden) * sizeof(float);
+  if (smem > 200 * 1024) CIE_FAIL("moe_route: a row of %d elements does not fit shared memory", hidden);
+  const int blocks = tokens;
   if (dtype == kFloat32) {
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      CIE_FAIL("moe_route: cannot reserve %zu bytes of shared memory", smem);
     CIE_LAUNCH("moe_route", moe_route_kernel<float>, dim3(blocks), dim3(warps * 32), smem, s, (const float*)x, router,
                correction, ids, weights, counts, tokens, hidden, experts, top, renormalize);
   } else if (dtype == kBFloat16) {
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      CIE_FAIL("moe_route: cannot reserve %zu bytes of shared memory", smem);
     CIE_LAUNCH("moe_route", moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, s,
                (const __nv_bfloat16*)x, router, correction, ids, weights, counts, tokens, hidden, experts, top,
                renormalize);
@@ -405,7 +446,7 @@ extern "C" int cie_moe_gate_up_simt(const void* x, const void* w_gate, const voi
                                     void* stream) {
   if (tokens <= 0) return 0;
   const int max_tiles = (tokens * top + kRowTile - 1) / kRowTile + experts;
-  dim3 grid((ff + 63) / 64, max_tiles);
+  dim3 grid((ff + 63) / 64, 2 * max_tiles);
   if (dtype == kFloat32) {
     CIE_LAUNCH("moe_gate_up", (moe_grouped_simt_kernel<float, true>), grid, dim3(256), 0, (cudaStream_t)stream,
                (const float*)x, (const float*)w_gate, (const float*)w_up, act, place_to_pair, tiles, tile_count, top,
@@ -426,7 +467,7 @@ extern "C" int cie_moe_down_simt(const void* act, const void* w_down, float* row
                                  int ff, int hidden, int dtype, void* stream) {
   if (tokens <= 0) return 0;
   const int max_tiles = (tokens * top + kRowTile - 1) / kRowTile + experts;
-  dim3 grid((hidden + 63) / 64, max_tiles);
+  dim3 grid((hidden + 63) / 64, 2 * max_tiles);
   if (dtype == kFloat32) {
     CIE_LAUNCH("moe_down", (moe_grouped_simt_kernel<float, false>), grid, dim3(256), 0, (cudaStream_t)stream,
                (const float*)act, (const float*)w_down, (const float*)nullptr, (void*)rows, place_to_pair, tiles,
@@ -443,16 +484,25 @@ extern "C" int cie_moe_down_simt(const void* act, const void* w_down, float* row
 
 // The same two products on the tensor cores: bfloat16 only, hidden and ff multiples of 8, pointers
 // aligned to 16 bytes (the caller checks).
+// w_up null: w_gate holds both, [experts][2 ff][hidden], interleaved in blocks of 16 rows.
 extern "C" int cie_moe_gate_up_tc(const void* x, const void* w_gate, const void* w_up, void* act,
                                   const int* place_to_pair, const int* tiles, const int* tile_count,
                                   int tokens, int top, int experts, int ff, int hidden, void* stream) {
+  if (!w_up && ff % 16) CIE_FAIL("moe_gate_up_tc: interleaved weights need a multiple of 16 channels, got %d", ff);
   if (tokens <= 0) return 0;
   if (hidden % 8 || ff % 8) CIE_FAIL("moe_gate_up_tc: sizes %d / %d are no multiples of 8", hidden, ff);
   const int max_tiles = (tokens * top + kRowTile - 1) / kRowTile + experts;
   dim3 grid((ff + kTcCols - 1) / kTcCols, max_tiles);
-  CIE_LAUNCH("moe_gate_up_tc", moe_grouped_tc_kernel<true>, grid, dim3(256), 0, (cudaStream_t)stream,
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(moe_grouped_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)moe_tc_smem<true>()) != cudaSuccess)
+      CIE_FAIL("moe_gate_up_tc: cannot reserve %zu bytes of shared memory", moe_tc_smem<true>());
+    configured = true;
+  }
+  CIE_LAUNCH("moe_gate_up_tc", moe_grouped_tc_kernel<true>, grid, dim3(256), moe_tc_smem<true>(), (cudaStream_t)stream,
              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, act, place_to_pair,
-             tiles, tile_count, top, ff, hidden);
+             tiles, tile_count, top, ff, hidden, w_up ? 0 : 1);
   return 0;
 }
 
@@ -463,9 +513,16 @@ extern "C" int cie_moe_down_tc(const void* act, const void* w_down, float* rows,
   if (hidden % 8 || ff % 8) CIE_FAIL("moe_down_tc: sizes %d / %d are no multiples of 8", hidden, ff);
   const int max_tiles = (tokens * top + kRowTile - 1) / kRowTile + experts;
   dim3 grid((hidden + kTcCols - 1) / kTcCols, max_tiles);
-  CIE_LAUNCH("moe_down_tc", moe_grouped_tc_kernel<false>, grid, dim3(256), 0, (cudaStream_t)stream,
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(moe_grouped_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)moe_tc_smem<false>()) != cudaSuccess)
+      CIE_FAIL("moe_down_tc: cannot reserve %zu bytes of shared memory", moe_tc_smem<false>());
+    configured = true;
+  }
+  CIE_LAUNCH("moe_down_tc", moe_grouped_tc_kernel<false>, grid, dim3(256), moe_tc_smem<false>(), (cudaStream_t)stream,
              (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, (const __nv_bfloat16*)nullptr, (void*)rows,
-             place_to_pair, tiles, tile_count, top, hidden, ff);
+             place_to_pair, tiles, tile_count, top, hidden, ff, 0);
   return 0;
 }
 

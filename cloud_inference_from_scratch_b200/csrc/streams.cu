@@ -60,7 +60,7 @@ __global__ void embedding_streams_kernel(const int* __restrict__ ids, const int*
 //   read     [S], or nullptr (ones: the plain sum of the streams)
 //   gain     [hidden], or one number when gain_single
 template <typename T, typename TU>
-__global__ void stream_norm_kernel(float* __restrict__ streams, int S, const TU* __restrict__ update,
+__global__ void __launch_bounds__(256) stream_norm_kernel(float* __restrict__ streams, int S, const TU* __restrict__ update,
                                    const float* __restrict__ mix, const float* __restrict__ out_w,
                                    const float* __restrict__ read, const float* __restrict__ gain,
                                    int gain_single, T* __restrict__ out, const int* __restrict__ rows,
@@ -237,7 +237,8 @@ extern "C" int cie_stream_norm(float* streams, int num_streams, const void* upda
   if (num_streams < 1 || num_streams > kMaxStreams) CIE_FAIL("stream_norm: 1..%d streams, got %d", kMaxStreams, num_streams);
   if (update && update_dtype != kFloat32 && update_dtype != dtype) CIE_FAIL("stream_norm: the update is float32 or of the activation type");
   const size_t smem = (size_t)hidden * sizeof(float);
-  const int threads = threads_for(hidden / 4) < 64 ? 64 : threads_for(hidden / 4);
+  int threads = threads_for(hidden / 4);
+  threads = threads < 64 ? 64 : (threads > 256 ? 256 : threads);
   DISPATCH_DTYPE(dtype, "stream_norm", {
     if (update_dtype == kFloat32) {
       if (allow_shared(stream_norm_kernel<T, float>, smem, "stream_norm")) return 1;

@@ -440,17 +440,41 @@ class Ops:
             self._moe_down_tc = lib.function("cie_moe_down_tc", [v, v, v, v, v, v, i, i, i, i, i, v])
             self.moe_row_tile = int(lib.handle.cie_moe_row_tile())
             self._moe_lib = lib
+            self._moe_tcgen05_lib = None
+
+    def _load_moe_tcgen05(self) -> None:
+        if self._moe_tcgen05_lib is None:
+            v, i = c_void_p, c_int
+            lib = _Lib(load_library("moe_tcgen05.cu"))
+            self._moe_gate_up_tcgen05 = lib.function(
+                "cie_moe_gate_up_tcgen05", [v, v, v, v, v, v, v, i, i, i, i, i, i, v, v])
+            self._moe_down_tcgen05 = lib.function(
+                "cie_moe_down_tcgen05", [v, v, v, v, v, v, i, i, i, i, i, i, v, v])
+            self._moe_tcgen05_lib = lib
+
+    def moe_interleaves(self, hidden: int, ff: int) -> bool:
+        """Whether the gate and up matrices of routed experts are kept as one tensor with their rows
+        interleaved in blocks of 16 ([E, 2F, H]), the layout of the tensor-core kernels that finish
+        SiLU(gate) * up in their epilogue."""
+        return self.code == BF16 and hidden % 8 == 0 and ff % 16 == 0
+
+    def interleave_gate_up(self, gate: Any, up: Any) -> Any:
+        """[E, F, H] twice -> [E, 2F, H]: 16 gate rows, their 16 up rows, the next 16 gate rows, ..."""
+        experts, ff, hidden = gate.shape
+        both = self.torch.stack([gate.view(experts, ff // 16, 16, hidden), up.view(experts, ff // 16, 16, hidden)], dim=2)
+        return both.reshape(experts, 2 * ff, hidden).contiguous()
 
     def routed_experts(self, x: Any, router: Any, correction: Any, w_gate: Any, w_up: Any, w_down: Any,
                        top: int, renormalize: bool, out: Any, workspace: Any) -> Any:
         """out[t] = sum over the ``top`` chosen experts e of score_e * down_e(SiLU(gate_e x) * up_e x).
-        ``router`` float32 [E, H]; ``w_gate``/``w_up`` [E, F, H]; ``w_down`` [E, H, F]; ``out`` float32
-        or the activation type."""
+        ``router`` float32 [E, H]; ``w_gate``/``w_up`` [E, F, H], or ``w_up`` None and ``w_gate`` the
+        interleaved [E, 2F, H] of ``interleave_gate_up``; ``w_down`` [E, H, F]; ``out`` float32 or the
+        activation type."""
         self._flush()
         self._load_moe()
         torch = self.torch
         tokens, hidden = x.shape
-        experts, ff = w_gate.shape[0], w_gate.shape[1]
+        experts, ff = w_gate.shape[0], w_gate.shape[1] // (2 if w_up is None else 1)
         pairs = tokens * top
         ids = workspace.get("moe.ids", tokens, top, torch.int32)
         weights = workspace.get("moe.weights", tokens, top, torch.float32)
@@ -469,8 +493,23 @@ class Ops:
         self._moe_route(_ptr(x), _ptr(router), _ptr(correction), _ptr(ids), _ptr(weights), _ptr(counts),
                         _ptr(offsets), _ptr(cursors), _ptr(place_to_pair), _ptr(tiles), _ptr(tile_count), tokens,
                         hidden, experts, top, 1 if renormalize else 0, code, self.stream)
-        if (code == BF16 and hidden % 8 == 0 and ff % 8 == 0 and os.environ.get("CIE_MOE_TC", "1") != "0"
-                and (x.data_ptr() | w_gate.data_ptr() | w_up.data_ptr() | w_down.data_ptr() | act.data_ptr()) % 16 == 0):
+        aligned = (x.data_ptr() | w_gate.data_ptr() | w_down.data_ptr() | act.data_ptr()) % 16 == 0
+        if w_up is None and not (code == BF16 and aligned):
+            raise KernelError("routed_experts: interleaved gate/up weights are for aligned bfloat16 operands")
+        if w_up is None and os.environ.get("CIE_MOE_TCGEN05", "1") != "0":
+            # tcgen05: the rows of every expert gathered side by side, tiles by TMA, accumulators in
+            # tensor memory
+            self._load_moe_tcgen05()
+            gathered = workspace.get("moe.sorted", tokens, top * hidden, self.dtype)
+            self._moe_gate_up_tcgen05(_ptr(x), _ptr(gathered), _ptr(w_gate), _ptr(act), _ptr(place_to_pair),
+                                      _ptr(tiles), _ptr(tile_count), tokens, top, experts, ff, hidden,
+                                      self.moe_row_tile, _ptr(self.error_word), self.stream)
+            self._moe_down_tcgen05(_ptr(act), _ptr(w_down), _ptr(rows), _ptr(place_to_pair), _ptr(tiles),
+                                   _ptr(tile_count), tokens, top, experts, ff, hidden, self.moe_row_tile,
+                                   _ptr(self.error_word), self.stream)
+            self.launches += 1
+        elif (code == BF16 and hidden % 8 == 0 and ff % 8 == 0 and aligned
+                and (w_up is None or (os.environ.get("CIE_MOE_TC", "1") != "0" and w_up.data_ptr() % 16 == 0))):
             # bfloat16 on the tensor cores (mma.sync, float32 accumulators)
             self._moe_gate_up_tc(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(act), _ptr(place_to_pair), _ptr(tiles),
                                  _ptr(tile_count), tokens, top, experts, ff, hidden, self.stream)

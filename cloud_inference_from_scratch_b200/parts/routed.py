@@ -7,7 +7,9 @@ sum 1 only if ``renormalize`` says so.  The result is the weighted sum of
 ``W_down (silu(W_gate h) * (W_up h))`` over the chosen experts, added up in float32 in the order
 the experts were chosen.
 
-The experts' matrices are stacked into three tensors at load time ([E, F, H], [E, F, H], [E, H, F]);
+The experts' matrices are stacked into three tensors at load time ([E, F, H], [E, F, H], [E, H, F];
+for bfloat16 with sizes the tensor-core kernels take, gate and up as one [E, 2F, H] with their rows
+interleaved in blocks of 16);
 the kernels group the (token, expert) pairs by expert on the device and never tell the host how
 many tokens an expert got, so a step is one fixed sequence of launches.
 """
@@ -54,6 +56,10 @@ class RoutedExperts(FeedForward):
         stack = lambda which: runtime.ops.prepare_weight(  # noqa: E731
             torch.stack([tensors[self._expert(e, which)] for e in range(self.num_experts)]))
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        if runtime.ops.moe_interleaves(self.hidden_size, self.intermediate_size):
+            # one tensor for gate and up, rows interleaved in blocks of 16: the tensor-core kernels
+            # finish SiLU(gate) * up in their epilogue
+            self.w_gate, self.w_up = runtime.ops.interleave_gate_up(self.w_gate, self.w_up), None
 
     def forward(self, x, ctx):
         import torch

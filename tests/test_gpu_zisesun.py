@@ -473,6 +473,34 @@ def test_routed_experts_part(dtype, count, top, tokens):
         assert not torch.allclose(plain.routed_experts(x.double(), p, dict(router=dict(experts=count, top=top))), want)
 
 
+@pytest.mark.parametrize("path", ["tcgen05", "mma.sync"])
+@pytest.mark.parametrize("hidden,ff,count,top,tokens", [(128, 48, 6, 2, 700), (64, 160, 3, 3, 150), (256, 16, 9, 4, 5)])
+def test_routed_experts_on_the_tensor_cores(monkeypatch, path, hidden, ff, count, top, tokens):
+    """bfloat16 with sizes the tensor-core kernels take (gate and up interleaved into one tensor):
+    several tiles of 128 rows an expert, experts with few rows or none, weight tiles that run past
+    an expert's last row."""
+    from cloud_inference_from_scratch_b200.config import PartSpec
+    from cloud_inference_from_scratch_b200.parts import build_part
+
+    if path == "mma.sync":
+        monkeypatch.setenv("CIE_MOE_TCGEN05", "0")
+    rt = runtime("bfloat16")
+    part = build_part("feed_forward", PartSpec("routed_experts", dict(hidden_size=hidden, intermediate_size=ff,
+                                                                      num_experts=count, top=top)))
+    tensors = {"router": rand(count, hidden, scale=0.3, seed=1), "correction": rand(count, scale=0.5, seed=2)}
+    for e in range(count):
+        tensors[f"e{e}.gate"] = rand(ff, hidden, scale=0.2, seed=10 + e).to(rt.dtype)
+        tensors[f"e{e}.up"] = rand(ff, hidden, scale=0.2, seed=30 + e).to(rt.dtype)
+        tensors[f"e{e}.down"] = rand(hidden, ff, scale=0.2, seed=50 + e).to(rt.dtype)
+    part.bind({name: value.cuda() for name, value in tensors.items()}, rt)
+    assert part.w_up is None and part.w_gate.shape == (count, 2 * ff, hidden)
+    x = rand(tokens, hidden, seed=3).to(rt.dtype)
+    got = part.forward(x.cuda(), None)
+    rt.ops.check_errors()
+    p = {"mlp." + name: value.double() for name, value in tensors.items()}
+    close(got, plain.routed_experts(x.double(), p, dict(router=dict(experts=count, top=top))), "bfloat16")
+
+
 # ------------------------------------------------------------------ the public entry point
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_engine(folders, dtype):
