@@ -607,7 +607,7 @@ def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int, only: st
     prompt = random_prompts(1, PROMPT_TOKENS, vocab, seed=99)[0]
     times = []
     launches = 0
-    for index in range(8):
+    for index in range(8 if only != "decode" else 4):
         core.step.admit("prefill")
         before = ops.launches
         with nvtx_range("bench.prefill"):

@@ -124,7 +124,19 @@ template <typename T> struct Vec16;
 template <> struct Vec16<float> { static constexpr int n = 4; };
 template <> struct Vec16<__nv_bfloat16> { static constexpr int n = 8; };
 
-template <typename T>
+__device__ __forceinline__ void stage16(void* dst, const void* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void stage_wait() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// kStaged: a warp first brings the key and value rows of its 32 keys into shared memory with
+// asynchronous 16-byte copies, all in flight at once (one trip to memory a block instead of one per
+// row piece), and reads them from there; rows of 16-bit elements whose sizes are multiples of 8.
+template <typename T, bool kStaged>
 __global__ void __launch_bounds__(kGroupWarps * 32)
 attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                        const T* __restrict__ k_pool, const T* __restrict__ v_pool,
@@ -139,6 +151,9 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   float* o_s = p_s + kGroupWarps * kGroupHeads * 32;         // [warps][kGroupHeads][kGroupMaxV]
   float* ml_s = o_s + kGroupWarps * kGroupHeads * kGroupMaxV;  // [warps][kGroupHeads][2]
   long long* slot_s = reinterpret_cast<long long*>(ml_s + kGroupWarps * kGroupHeads * 2);   // [warps][32]
+  const int k_ld = dim + 16 / (int)sizeof(T);          // staged key rows are padded by 16 bytes: no bank conflicts
+  T* k_stage = reinterpret_cast<T*>(slot_s + kGroupWarps * 32);                 // [warps][32][k_ld]
+  T* v_stage = k_stage + (size_t)kGroupWarps * 32 * k_ld;                      // [warps][32][vdim]
   pdl_wait();
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,8 +197,18 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     float dot[kGroupHeads];
 #pragma unroll
     for (int h = 0; h < kGroupHeads; ++h) dot[h] = 0.f;
+    T* my_k = k_stage + ((size_t)warp * 32 + lane) * k_ld;
+    T* my_v = v_stage + (size_t)warp * 32 * vdim;
+    if constexpr (kStaged) {
+      if (slot >= 0) {
+        for (int d0 = 0; d0 < dim; d0 += V) stage16(my_k + d0, k_pool + slot * dim + d0);
+        for (int d0 = 0; d0 < vdim; d0 += V) stage16(my_v + (size_t)lane * vdim + d0, v_pool + slot * vdim + d0);
+      }
+      stage_wait();
+      __syncwarp();
+    }
     if (slot >= 0) {
-      const T* kr = k_pool + slot * dim;
+      const T* kr = kStaged ? my_k : k_pool + slot * dim;
       for (int d0 = 0; d0 < dim; d0 += V) {
         const uint4 raw = *reinterpret_cast<const uint4*>(kr + d0);
         const T* kv = reinterpret_cast<const T*>(&raw);
@@ -218,7 +243,7 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     for (int j = 0; j < count; ++j) {
       const long long o = my_slot[j];
       if (o < 0) continue;
-      const T* vr = v_pool + o * vdim;
+      const T* vr = kStaged ? my_v + (size_t)j * vdim : v_pool + o * vdim;
       float vv[kGroupMaxV / 32];
 #pragma unroll
       for (int c = 0; c < kGroupMaxV / 32; ++c) vv[c] = lane + 32 * c < vdim ? to_float(vr[lane + 32 * c]) : 0.f;
@@ -286,24 +311,26 @@ extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, 
   if (grouped && dim % vec == 0 && vdim <= kGroupMaxV && (dtype == kFloat32 || dtype == kBFloat16) &&
       (reinterpret_cast<uintptr_t>(k_pool) & 15) == 0) {
     const int group = q_heads / kv_heads;
-    const size_t smem = sizeof(float) * ((size_t)kGroupHeads * dim + kGroupWarps * kGroupHeads * (32 + kGroupMaxV + 2)) +
+    const size_t base = sizeof(float) * ((size_t)kGroupHeads * dim + kGroupWarps * kGroupHeads * (32 + kGroupMaxV + 2)) +
                         sizeof(long long) * kGroupWarps * 32;
+    // bfloat16 rows are staged in shared memory where value rows, too, are whole 16-byte pieces
+    const bool staged = dtype == kBFloat16 && vdim % 8 == 0 && (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0;
+    const size_t smem = base + (staged ? (size_t)kGroupWarps * 32 * (dim + 8 + vdim) * sizeof(__nv_bfloat16) : 0);
     dim3 grid(tokens, kv_heads, (group + kGroupHeads - 1) / kGroupHeads);
-    if (dtype == kFloat32) {
-      if (cudaFuncSetAttribute(attention_group_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        CIE_FAIL("attention_generic: cannot reserve %zu bytes of shared memory", smem);
-      CIE_LAUNCH("attention_group", attention_group_kernel<float>, grid, dim3(kGroupWarps * 32), smem, s,
-          (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool, positions,
-          request_of_token, table, table_width, num_pages, q_heads, kv_heads, dim, vdim, page_size, scale, window,
-          r1, r2, err);
-    } else {
-      if (cudaFuncSetAttribute(attention_group_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        CIE_FAIL("attention_generic: cannot reserve %zu bytes of shared memory", smem);
-      CIE_LAUNCH("attention_group", attention_group_kernel<__nv_bfloat16>, grid, dim3(kGroupWarps * 32), smem, s,
-          (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
-          (const __nv_bfloat16*)v_pool, positions, request_of_token, table, table_width, num_pages, q_heads,
-          kv_heads, dim, vdim, page_size, scale, window, r1, r2, err);
-    }
+#define CIE_GROUP(T, S)                                                                                            \
+  do {                                                                                                             \
+    if (cudaFuncSetAttribute(attention_group_kernel<T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                             (int)smem) != cudaSuccess)                                                            \
+      CIE_FAIL("attention_generic: cannot reserve %zu bytes of shared memory", smem);                              \
+    CIE_LAUNCH("attention_group", (attention_group_kernel<T, S>), grid, dim3(kGroupWarps * 32), smem, s,            \
+               (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, positions,          \
+               request_of_token, table, table_width, num_pages, q_heads, kv_heads, dim, vdim, page_size, scale,    \
+               window, r1, r2, err);                                                                               \
+  } while (0)
+    if (dtype == kFloat32) CIE_GROUP(float, false);
+    else if (staged) CIE_GROUP(__nv_bfloat16, true);
+    else CIE_GROUP(__nv_bfloat16, false);
+#undef CIE_GROUP
     return 0;
   }
   if (dtype == kFloat32) {

@@ -28,7 +28,7 @@ constexpr int kRowTile = 128;         // rows of a tile of the grouped products
 // share the experts (a lane strides over the row with 16-byte loads of the router matrix where the
 // row length allows), then the first warp turns logits into scores and chooses.
 // ids / weights: [tokens][top]; counts[e] += 1 per choice.
-constexpr int kRouteWarps = 4;
+constexpr int kRouteWarps = 8;
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router,
@@ -51,13 +51,22 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router,
     const float* w = router + (size_t)e * hidden;
     float dot = 0.f;
     if (wide) {
-      for (int k = 4 * lane; k < hidden; k += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(w + k);
-        const float4 xv = *reinterpret_cast<const float4*>(row_s + k);
-        dot = fmaf(xv.x, wv.x, dot);
-        dot = fmaf(xv.y, wv.y, dot);
-        dot = fmaf(xv.z, wv.z, dot);
-        dot = fmaf(xv.w, wv.w, dot);
+      // eight 16-byte loads of the router row are asked for before the first is used: the row comes
+      // from memory once a step and nothing else hides that trip
+      for (int k0 = 4 * lane; k0 < hidden; k0 += 8 * 128) {
+        float4 wv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          wv[u] = k0 + 128 * u < hidden ? *reinterpret_cast<const float4*>(w + k0 + 128 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (k0 + 128 * u >= hidden) break;
+          const float4 xv = *reinterpret_cast<const float4*>(row_s + k0 + 128 * u);
+          dot = fmaf(xv.x, wv[u].x, dot);
+          dot = fmaf(xv.y, wv[u].y, dot);
+          dot = fmaf(xv.z, wv[u].z, dot);
+          dot = fmaf(xv.w, wv[u].w, dot);
+        }
       }
     } else {
       for (int k = lane; k < hidden; k += 32) dot = fmaf(row_s[k], w[k], dot);
