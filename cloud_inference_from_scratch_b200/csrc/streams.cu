@@ -17,7 +17,7 @@ CIE_DEFINE_LAST_ERROR()
 
 namespace cie {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 
 // ---------------------------------------------------------------- embedding
 template <typename T>
@@ -59,7 +59,8 @@ __global__ void embedding_streams_kernel(const int* __restrict__ ids, const int*
 //   out_w    [S], or nullptr (ones)
 //   read     [S], or nullptr (ones: the plain sum of the streams)
 //   gain     [hidden], or one number when gain_single
-template <typename T, typename TU>
+// MAXS: the most streams the instance takes (its loops are unrolled to that many).
+template <typename T, typename TU, int MAXS>
 __global__ void __launch_bounds__(256) stream_norm_kernel(float* __restrict__ streams, int S, const TU* __restrict__ update,
                                    const float* __restrict__ mix, const float* __restrict__ out_w,
                                    const float* __restrict__ read, const float* __restrict__ gain,
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(float* __restrict__ st
   __shared__ float mix_s[kMaxStreams * kMaxStreams], out_s[kMaxStreams], read_s[kMaxStreams];
   pdl_trigger();   // what follows is a matrix product that only asks for weights before its own wait
   pdl_wait();
-  if (threadIdx.x < S * S) mix_s[threadIdx.x] = mix ? mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.f : 0.f);
+  for (int e = threadIdx.x; e < S * S; e += blockDim.x) mix_s[e] = mix ? mix[e] : (e / S == e % S ? 1.f : 0.f);
   if (threadIdx.x < S) {
     out_s[threadIdx.x] = out_w ? out_w[threadIdx.x] : 1.f;
     read_s[threadIdx.x] = read ? read[threadIdx.x] : 1.f;
@@ -83,18 +84,18 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(float* __restrict__ st
   const bool write_back = rows == nullptr && update != nullptr;
   float sumsq = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float x[kMaxStreams];
+    float x[MAXS];
 #pragma unroll
-    for (int s = 0; s < kMaxStreams; ++s) x[s] = s < S ? base[(size_t)s * hidden + i] : 0.f;
+    for (int s = 0; s < MAXS; ++s) x[s] = s < S ? base[(size_t)s * hidden + i] : 0.f;
     float u = 0.f;
     if (y_row) {
       const float y = to_float(y_row[i]);
 #pragma unroll
-      for (int t = 0; t < kMaxStreams; ++t) {
+      for (int t = 0; t < MAXS; ++t) {
         if (t >= S) break;
         float v = 0.f;
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s)
+        for (int s = 0; s < MAXS; ++s)
           if (s < S) v = fmaf(mix_s[s * S + t], x[s], v);
         v = fmaf(out_s[t], y, v);
         if (write_back) base[(size_t)t * hidden + i] = v;
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(float* __restrict__ st
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < kMaxStreams; ++t)
+      for (int t = 0; t < MAXS; ++t)
         if (t < S) u = fmaf(read_s[t], x[t], u);
     }
     u_s[i] = u;
@@ -239,17 +240,24 @@ extern "C" int cie_stream_norm(float* streams, int num_streams, const void* upda
   const size_t smem = (size_t)hidden * sizeof(float);
   int threads = threads_for(hidden / 4);
   threads = threads < 64 ? 64 : (threads > 256 ? 256 : threads);
+#define CIE_STREAM_NORM(T, TU, MAXS)                                                                          \
+  do {                                                                                                         \
+    if (allow_shared(stream_norm_kernel<T, TU, MAXS>, smem, "stream_norm")) return 1;                          \
+    CIE_LAUNCH("stream_norm", (stream_norm_kernel<T, TU, MAXS>), dim3(count), dim3(threads), smem,             \
+               (cudaStream_t)stream, streams, num_streams, (const TU*)update, mix, out_w, read, gain,          \
+               gain_single, (T*)out, rows, hidden, eps);                                                       \
+  } while (0)
+  // up to four streams (the usual few) run an instance whose loops are unrolled to four
   DISPATCH_DTYPE(dtype, "stream_norm", {
     if (update_dtype == kFloat32) {
-      if (allow_shared(stream_norm_kernel<T, float>, smem, "stream_norm")) return 1;
-      CIE_LAUNCH("stream_norm", (stream_norm_kernel<T, float>), dim3(count), dim3(threads), smem, (cudaStream_t)stream,
-                 streams, num_streams, (const float*)update, mix, out_w, read, gain, gain_single, (T*)out, rows, hidden, eps);
+      if (num_streams <= 4) CIE_STREAM_NORM(T, float, 4);
+      else CIE_STREAM_NORM(T, float, kMaxStreams);
     } else {
-      if (allow_shared(stream_norm_kernel<T, T>, smem, "stream_norm")) return 1;
-      CIE_LAUNCH("stream_norm", (stream_norm_kernel<T, T>), dim3(count), dim3(threads), smem, (cudaStream_t)stream,
-                 streams, num_streams, (const T*)update, mix, out_w, read, gain, gain_single, (T*)out, rows, hidden, eps);
+      if (num_streams <= 4) CIE_STREAM_NORM(T, T, 4);
+      else CIE_STREAM_NORM(T, T, kMaxStreams);
     }
   })
+#undef CIE_STREAM_NORM
   return 0;
 }
 

@@ -231,7 +231,7 @@ def test_embedding_adds_the_position_vector_into_every_stream(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("streams,hidden", [(1, 40), (2, 96), (4, 1000), (8, 33)])
+@pytest.mark.parametrize("streams,hidden", [(1, 40), (2, 96), (4, 1000), (8, 33), (16, 2048)])
 def test_hyper_connection_write_read_and_single_gain_norm(dtype, streams, hidden):
     """The kernel between two sublayers against the oracle's hyper_sublayer, with a mix matrix that is
     not symmetric (so [from, to] and [to, from] differ)."""
