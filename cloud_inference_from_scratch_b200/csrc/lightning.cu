@@ -107,12 +107,40 @@ constexpr int kChunkCols = kChunkDim / 32;              // value columns of a la
 
 __device__ __forceinline__ float decay_power(float log2_decay, int n) { return n == 0 ? 1.f : exp2f(log2_decay * (float)n); }
 
+template <typename T> struct Piece;                 // a 16-byte piece of a row
+template <> struct Piece<float> { static constexpr int n = 4; };
+template <> struct Piece<__nv_bfloat16> { static constexpr int n = 8; };
+
+// dst[j * ld + i] = SiLU(proj[row0 + j][col0 + i]) * factor(j) for j < n, i < width: 16-byte loads where
+// the columns allow (one index division per piece instead of per element), else element by element.
+template <typename T, typename Factor>
+__device__ __forceinline__ void stage_silu(float* __restrict__ dst, int ld, const T* __restrict__ proj, int proj_stride,
+                                           int row0, int n, int col0, int width, Factor factor) {
+  constexpr int V = Piece<T>::n;
+  if (width % V == 0 && col0 % V == 0 && proj_stride % V == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0) {
+    const int pieces = width / V;
+    for (int e = threadIdx.x; e < n * pieces; e += blockDim.x) {
+      const int j = e / pieces, i = (e % pieces) * V;
+      const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)(row0 + j) * proj_stride + col0 + i);
+      const T* v = reinterpret_cast<const T*>(&raw);
+      const float f = factor(j);
+#pragma unroll
+      for (int x = 0; x < V; ++x) dst[j * ld + i + x] = silu_f(to_float(v[x])) * f;
+    }
+    return;
+  }
+  for (int e = threadIdx.x; e < n * width; e += blockDim.x) {
+    const int j = e / width, i = e % width;
+    dst[j * ld + i] = silu_f(to_float(proj[(size_t)(row0 + j) * proj_stride + col0 + i])) * factor(j);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kScanWarps * 32)
 lightning_chunk_state_kernel(const T* __restrict__ proj, int proj_stride, float* __restrict__ chunk_state,
                              const float* __restrict__ decay, const int* __restrict__ chunk_row,
                              const int* __restrict__ chunk_count, int heads, int dim, int vdim) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   float* k_s = smem;                          // [kChunk][dim], times decay^(n-1-j)
   float* v_s = smem + kChunk * dim;           // [kChunk][vdim]
   pdl_wait();
@@ -121,33 +149,38 @@ lightning_chunk_state_kernel(const T* __restrict__ proj, int proj_stride, float*
   const int row0 = chunk_row[chunk], n = chunk_count[chunk];
   const float log2_d = log2f(decay[head]);
   const int k_off = heads * dim + head * dim, v_off = 2 * heads * dim + head * vdim;
-  for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
-    const int j = e / dim, i = e % dim;
-    k_s[e] = silu_f(to_float(proj[(size_t)(row0 + j) * proj_stride + k_off + i])) * decay_power(log2_d, n - 1 - j);
-  }
-  for (int e = threadIdx.x; e < n * vdim; e += blockDim.x) {
-    const int j = e / vdim, c = e % vdim;
-    v_s[e] = silu_f(to_float(proj[(size_t)(row0 + j) * proj_stride + v_off + c]));
-  }
+  stage_silu(k_s, dim, proj, proj_stride, row0, n, k_off, dim, [&](int j) { return decay_power(log2_d, n - 1 - j); });
+  stage_silu(v_s, vdim, proj, proj_stride, row0, n, v_off, vdim, [](int) { return 1.f; });
   __syncthreads();
+  // a warp owns kChunkRows state rows that follow each other (its k values come as 16-byte loads), a
+  // lane the value columns lane, lane + 32, ...
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i0 = warp * kChunkRows;
+  const bool whole = dim % 4 == 0 && i0 + kChunkRows <= dim;
   float u[kChunkRows][kChunkCols] = {};
   for (int j = 0; j < n; ++j) {
-    float vv[kChunkCols];
+    float vv[kChunkCols], kv[kChunkRows];
 #pragma unroll
     for (int c = 0; c < kChunkCols; ++c) vv[c] = lane + 32 * c < vdim ? v_s[j * vdim + lane + 32 * c] : 0.f;
+    if (whole) {
 #pragma unroll
-    for (int r = 0; r < kChunkRows; ++r) {
-      const int i = warp + kScanWarps * r;
-      const float kv = i < dim ? k_s[j * dim + i] : 0.f;
+      for (int r = 0; r < kChunkRows; r += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(k_s + j * dim + i0 + r);
+        kv[r] = k4.x; kv[r + 1] = k4.y; kv[r + 2] = k4.z; kv[r + 3] = k4.w;
+      }
+    } else {
 #pragma unroll
-      for (int c = 0; c < kChunkCols; ++c) u[r][c] = fmaf(kv, vv[c], u[r][c]);
+      for (int r = 0; r < kChunkRows; ++r) kv[r] = i0 + r < dim ? k_s[j * dim + i0 + r] : 0.f;
     }
+#pragma unroll
+    for (int r = 0; r < kChunkRows; ++r)
+#pragma unroll
+      for (int c = 0; c < kChunkCols; ++c) u[r][c] = fmaf(kv[r], vv[c], u[r][c]);
   }
   float* dst = chunk_state + ((size_t)chunk * heads + head) * dim * vdim;
 #pragma unroll
   for (int r = 0; r < kChunkRows; ++r) {
-    const int i = warp + kScanWarps * r;
+    const int i = i0 + r;
     if (i >= dim) continue;
 #pragma unroll
     for (int c = 0; c < kChunkCols; ++c)
@@ -206,7 +239,7 @@ lightning_chunk_output_kernel(const T* __restrict__ proj, int proj_stride, float
                               const float* __restrict__ chunk_state, const float* __restrict__ decay,
                               const int* __restrict__ chunk_row, const int* __restrict__ chunk_count, int heads,
                               int dim, int vdim) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   float* q_s = smem;                              // [kChunk][dim]
   float* k_s = q_s + kChunk * dim;                // [kChunk][dim + 1]
   float* v_s = k_s + kChunk * (dim + 1);          // [kChunk][vdim]
@@ -217,16 +250,9 @@ lightning_chunk_output_kernel(const T* __restrict__ proj, int proj_stride, float
   const int row0 = chunk_row[chunk], n = chunk_count[chunk];
   const float log2_d = log2f(decay[head]);
   const int q_off = head * dim, k_off = heads * dim + head * dim, v_off = 2 * heads * dim + head * vdim;
-  for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
-    const int j = e / dim, i = e % dim;
-    const T* row = proj + (size_t)(row0 + j) * proj_stride;
-    q_s[j * dim + i] = silu_f(to_float(row[q_off + i]));
-    k_s[j * (dim + 1) + i] = silu_f(to_float(row[k_off + i]));
-  }
-  for (int e = threadIdx.x; e < n * vdim; e += blockDim.x) {
-    const int j = e / vdim, c = e % vdim;
-    v_s[e] = silu_f(to_float(proj[(size_t)(row0 + j) * proj_stride + v_off + c]));
-  }
+  stage_silu(q_s, dim, proj, proj_stride, row0, n, q_off, dim, [](int) { return 1.f; });
+  stage_silu(k_s, dim + 1, proj, proj_stride, row0, n, k_off, dim, [](int) { return 1.f; });
+  stage_silu(v_s, vdim, proj, proj_stride, row0, n, v_off, vdim, [](int) { return 1.f; });
   __syncthreads();
   // a[i][j] = decay^(i-j) q_i.k_j for j <= i (lanes run over j: k rows are padded by one element)
   for (int e = threadIdx.x; e < n * kChunk; e += blockDim.x) {
@@ -244,7 +270,27 @@ lightning_chunk_output_kernel(const T* __restrict__ proj, int proj_stride, float
   // a warp takes tokens warp, warp + 8, ...; a lane the value columns lane, lane + 32, ...
   constexpr int kTokens = kChunk / kScanWarps;
   float inter[kTokens][kChunkCols] = {}, intra[kTokens][kChunkCols] = {};
-  for (int x = 0; x < dim; ++x) {
+  const int dim4 = dim % 4 == 0 ? dim : 0;       // four state rows a step where the q rows allow 16-byte loads
+  for (int x = 0; x < dim4; x += 4) {
+    float sv[4][kChunkCols];
+#pragma unroll
+    for (int y = 0; y < 4; ++y)
+#pragma unroll
+      for (int c = 0; c < kChunkCols; ++c) sv[y][c] = lane + 32 * c < vdim ? before[(size_t)(x + y) * vdim + lane + 32 * c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t) {
+      const int i = warp + kScanWarps * t;
+      const float4 q4 = i < n ? *reinterpret_cast<const float4*>(q_s + i * dim + x) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < kChunkCols; ++c) {
+        inter[t][c] = fmaf(q4.x, sv[0][c], inter[t][c]);
+        inter[t][c] = fmaf(q4.y, sv[1][c], inter[t][c]);
+        inter[t][c] = fmaf(q4.z, sv[2][c], inter[t][c]);
+        inter[t][c] = fmaf(q4.w, sv[3][c], inter[t][c]);
+      }
+    }
+  }
+  for (int x = dim4; x < dim; ++x) {
     float sv[kChunkCols];
 #pragma unroll
     for (int c = 0; c < kChunkCols; ++c) sv[c] = lane + 32 * c < vdim ? before[(size_t)x * vdim + lane + 32 * c] : 0.f;
