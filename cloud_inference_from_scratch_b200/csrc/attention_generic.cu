@@ -143,7 +143,11 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const int* __restrict__ positions, const int* __restrict__ request_of_token,
                        const int* __restrict__ table, int table_width, int num_pages, int q_heads,
                        int kv_heads, int dim, int vdim, int page_size, float scale, int window,
-                       const float* __restrict__ r1, const float* __restrict__ r2, int* err) {
+                       const float* __restrict__ r1, const float* __restrict__ r2, int splits,
+                       float* __restrict__ shares, int* __restrict__ tickets, int* err) {
+  // splits > 1: the keys of a token are cut into that many ranges, one CTA each (blockIdx.x = token *
+  // splits + range); a CTA leaves its maximum, sum and unnormalised output in `shares`, and whoever
+  // draws the unit's last ticket joins them in range order (tickets are zero between launches)
   constexpr int V = Vec16<T>::n;
   extern __shared__ __align__(16) float group_smem[];
   float* q_s = group_smem;                                   // [kGroupHeads][dim]
@@ -157,13 +161,16 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   pdl_wait();
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x, kvh = blockIdx.y;
+  const int t = blockIdx.x / splits, split = blockIdx.x % splits, kvh = blockIdx.y;
   const int group = q_heads / kv_heads;
   const int h0 = blockIdx.z * kGroupHeads, heads = min(kGroupHeads, group - h0);
   const int pos = positions[t];
   const int* row = table + (size_t)request_of_token[t] * table_width;
   const int length = pos + 1;
   const int first = (window > 0 && length > window) ? length - window : 0;
+  // this CTA's keys: whole blocks of 32, counted from the first visible key
+  const int per = ((length - first + splits - 1) / splits + 31) / 32 * 32;
+  const int my_first = first + split * per, my_end = min(length, my_first + per);
   for (int e = threadIdx.x; e < kGroupHeads * dim; e += blockDim.x) {
     const int h = e / dim, d = e % dim;
     q_s[e] = h < heads ? to_float(q[(size_t)t * q_stride + (size_t)(kvh * group + h0 + h) * dim + d]) : 0.f;
@@ -185,10 +192,10 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   }
   float* my_p = p_s + warp * kGroupHeads * 32;
   long long* my_slot = slot_s + warp * 32;
-  for (int base = first + warp * 32; base < length; base += kGroupWarps * 32) {
+  for (int base = my_first + warp * 32; base < my_end; base += kGroupWarps * 32) {
     const int key = base + lane;
     long long slot = -1;
-    if (key < length) {
+    if (key < my_end) {
       const int index = key / page_size;
       const int page = index < table_width ? row[index] : -1;
       if (page < 0 || page >= num_pages) atomicOr(err, kErrBadPage);
@@ -239,7 +246,7 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     }
     my_slot[lane] = slot;
     __syncwarp();
-    const int count = min(32, length - base);
+    const int count = min(32, my_end - base);
     for (int j = 0; j < count; ++j) {
       const long long o = my_slot[j];
       if (o < 0) continue;
@@ -267,6 +274,9 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     }
   }
   __syncthreads();
+  const size_t unit = ((size_t)t * kv_heads + kvh) * gridDim.z + blockIdx.z;
+  constexpr int kShare = kGroupMaxV + 2;      // floats of one head's share: output, then maximum and sum
+  float* my_share = shares ? shares + (unit * splits + split) * kGroupHeads * kShare : nullptr;
   for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
     const int h = e / vdim, d = e % vdim;
     float top = -FLT_MAX;
@@ -279,6 +289,40 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
       sum = fmaf(share, ml_s[(w * kGroupHeads + h) * 2 + 1], sum);
       value = fmaf(share, o_s[(w * kGroupHeads + h) * kGroupMaxV + d], value);
     }
+    if (splits == 1) {
+      out[(size_t)t * out_stride + (size_t)(kvh * group + h0 + h) * vdim + d] = from_float<T>(sum > 0.f ? value / sum : 0.f);
+    } else {
+      my_share[h * kShare + d] = value;
+      if (d == 0) {
+        my_share[h * kShare + kGroupMaxV] = top;
+        my_share[h * kShare + kGroupMaxV + 1] = sum;
+      }
+    }
+  }
+  if (splits == 1) return;
+  __shared__ int last_s;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(tickets + unit, 1);
+    last_s = ticket == splits - 1;
+    if (last_s) tickets[unit] = 0;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  const float* unit_shares = shares + unit * splits * kGroupHeads * kShare;
+  for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
+    const int h = e / vdim, d = e % vdim;
+    float top = -FLT_MAX;
+    for (int r = 0; r < splits; ++r) top = fmaxf(top, __ldcg(unit_shares + (r * kGroupHeads + h) * kShare + kGroupMaxV));
+    float sum = 0.f, value = 0.f;
+    for (int r = 0; r < splits; ++r) {
+      const float* part = unit_shares + (r * kGroupHeads + h) * kShare;
+      const float share = expf(__ldcg(part + kGroupMaxV) - top);
+      sum = fmaf(share, __ldcg(part + kGroupMaxV + 1), sum);
+      value = fmaf(share, __ldcg(part + d), value);
+    }
     out[(size_t)t * out_stride + (size_t)(kvh * group + h0 + h) * vdim + d] = from_float<T>(sum > 0.f ? value / sum : 0.f);
   }
 }
@@ -287,16 +331,23 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
 
 using namespace cie;
 
+extern "C" int cie_attention_group_share_floats() { return kGroupHeads * (kGroupMaxV + 2); }
+
 // q: rows of q_stride elements, query head h of token t at q[t*q_stride + h*dim].
 // out: [tokens, out_stride], head h at column h*vdim.  Pools: [pages][kv_heads][page_size][dim or vdim].
-extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, int out_stride,
-                                        const void* k_pool, const void* v_pool, const int* positions,
-                                        const int* request_of_token, const int* table, int table_width,
-                                        int num_pages, int tokens, int q_heads, int kv_heads, int dim,
-                                        int vdim, int page_size, float scale, int window,
-                                        const float* r1, const float* r2, int dtype, int* err,
-                                        void* stream) {
+// splits > 1 (the kernel that shares keys among a group's heads only; ignored otherwise): a token's
+// keys are cut into that many ranges with a CTA each; `shares` holds tokens * kv_heads *
+// ceil(group / 8) * splits * cie_attention_group_share_floats() floats and `tickets` one int, zero, per
+// (token, kv head, 8 heads).
+extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* out, int out_stride,
+                                           const void* k_pool, const void* v_pool, const int* positions,
+                                           const int* request_of_token, const int* table, int table_width,
+                                           int num_pages, int tokens, int q_heads, int kv_heads, int dim,
+                                           int vdim, int page_size, float scale, int window,
+                                           const float* r1, const float* r2, int splits, float* shares,
+                                           int* tickets, int dtype, int* err, void* stream) {
   if (tokens <= 0) return 0;
+  if (splits < 1 || (splits > 1 && (!shares || !tickets))) CIE_FAIL("attention_generic: %d key ranges need shares and tickets", splits);
   if (dim > kMaxDim || dim < 1 || vdim > kMaxDim || vdim < 1)
     CIE_FAIL("attention_generic: head sizes %d / %d are outside 1..%d", dim, vdim, kMaxDim);
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_generic: %d query heads do not divide over %d kv heads", q_heads, kv_heads);
@@ -316,7 +367,7 @@ extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, 
     // bfloat16 rows are staged in shared memory where value rows, too, are whole 16-byte pieces
     const bool staged = dtype == kBFloat16 && vdim % 8 == 0 && (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0;
     const size_t smem = base + (staged ? (size_t)kGroupWarps * 32 * (dim + 8 + vdim) * sizeof(__nv_bfloat16) : 0);
-    dim3 grid(tokens, kv_heads, (group + kGroupHeads - 1) / kGroupHeads);
+    dim3 grid(tokens * splits, kv_heads, (group + kGroupHeads - 1) / kGroupHeads);
 #define CIE_GROUP(T, S)                                                                                            \
   do {                                                                                                             \
     if (cudaFuncSetAttribute(attention_group_kernel<T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
@@ -325,7 +376,7 @@ extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, 
     CIE_LAUNCH("attention_group", (attention_group_kernel<T, S>), grid, dim3(kGroupWarps * 32), smem, s,            \
                (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, positions,          \
                request_of_token, table, table_width, num_pages, q_heads, kv_heads, dim, vdim, page_size, scale,    \
-               window, r1, r2, err);                                                                               \
+               window, r1, r2, splits, shares, tickets, err);                                                      \
   } while (0)
     if (dtype == kFloat32) CIE_GROUP(float, false);
     else if (staged) CIE_GROUP(__nv_bfloat16, true);
@@ -347,6 +398,18 @@ extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, 
     CIE_FAIL("attention_generic: unknown element type code %d", dtype);
   }
   return 0;
+}
+
+extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* k_pool, const void* v_pool, const int* positions,
+                                        const int* request_of_token, const int* table, int table_width,
+                                        int num_pages, int tokens, int q_heads, int kv_heads, int dim,
+                                        int vdim, int page_size, float scale, int window,
+                                        const float* r1, const float* r2, int dtype, int* err,
+                                        void* stream) {
+  return cie_attention_generic_split(q, q_stride, out, out_stride, k_pool, v_pool, positions, request_of_token,
+                                     table, table_width, num_pages, tokens, q_heads, kv_heads, dim, vdim,
+                                     page_size, scale, window, r1, r2, 1, nullptr, nullptr, dtype, err, stream);
 }
 
 extern "C" int cie_attention_generic(const void* q, int q_stride, void* out, int out_stride,

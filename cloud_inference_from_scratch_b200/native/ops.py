@@ -106,6 +106,12 @@ class Ops:
             "cie_attention_generic_ex",
             [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v],
         )
+        self._attention_generic_split = ag.function(
+            "cie_attention_generic_split",
+            [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v, i, v, v],
+        )
+        self._group_share_floats = int(ag.handle.cie_attention_group_share_floats())
+        self._group_tickets = None
         # libraries that only some models need are built and loaded when a part first asks for them
         self._streams_lib = None
         self._lightning_lib = None
@@ -207,11 +213,12 @@ class Ops:
         if (fast is None or singles == ctx.num_requests or q.shape[1] % 8 or out.shape[1] % 8
                 or os.environ.get("CIE_PENALISED_TC", "1") == "0"):
             self.attention_generic(q, out, ctx, kv, q_heads, kv_heads, head_dim, scale, window,
-                                   value_dim=value_dim, distance=distance)
+                                   value_dim=value_dim, distance=distance,
+                                   few_tokens=singles == ctx.num_requests)
             return
         if singles:     # the leading rows of a mixed step are its single tokens
             self.attention_generic(q[:singles], out[:singles], ctx, kv, q_heads, kv_heads, head_dim, scale,
-                                   window, value_dim=value_dim, distance=distance)
+                                   window, value_dim=value_dim, distance=distance, few_tokens=True)
         plan = ctx.extras.get(("attention", q_heads // kv_heads)) or None
         fast.run_portions(q, out, ctx, kv, q_heads, kv_heads, scale, window, plan, distance, True)
 
@@ -866,12 +873,34 @@ class Ops:
 
     def attention_generic(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int,
                           kv_heads: int, head_dim: int, scale: float, window: int,
-                          value_dim: int | None = None, distance: Any = None) -> None:
+                          value_dim: int | None = None, distance: Any = None, few_tokens: bool = False) -> None:
         """``value_dim``: size of a value head when it is not ``head_dim``; ``distance``: (r1, r2),
-        float32 [q_heads] each, of the penalty r1 * log(1 + r2 * (query position - key position))."""
+        float32 [q_heads] each, of the penalty r1 * log(1 + r2 * (query position - key position)).
+        ``few_tokens``: the rows are single tokens of a decode step; their keys are then cut into
+        ranges with a CTA each where the device would otherwise stand mostly idle."""
         self._flush()
         table = ctx.block_tables[kv.group]
         self.launches += 1
+        if few_tokens:
+            tokens = qkv.shape[0]
+            units = tokens * kv_heads * -(-(q_heads // kv_heads) // 8)
+            keys = table.shape[1] * kv.page_size
+            if window > 0:
+                keys = min(keys, window)
+            # a range keeps at least 128 keys; no more CTAs than one an SM
+            splits = max(1, min(keys // 128, self.sm_count // max(units, 1), 16))
+            if splits > 1:
+                r1, r2 = distance if distance is not None else (None, None)
+                shares = self.scratch("attention.shares", units * splits * self._group_share_floats)
+                if self._group_tickets is None or self._group_tickets.numel() < units:
+                    self._group_tickets = self.torch.zeros(max(units, 1024), dtype=self.torch.int32, device=self.device)
+                    self.scratch_generation += 1
+                self._attention_generic_split(
+                    _ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions),
+                    _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, tokens, q_heads, kv_heads,
+                    head_dim, value_dim or head_dim, kv.page_size, scale, window, _ptr(r1), _ptr(r2), splits,
+                    _ptr(shares), _ptr(self._group_tickets), self._code_of(qkv), _ptr(self.error_word), self.stream)
+                return
         if distance is not None or (value_dim or head_dim) != head_dim:
             r1, r2 = distance if distance is not None else (None, None)
             self._attention_generic_ex(_ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k),

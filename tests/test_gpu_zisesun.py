@@ -362,15 +362,18 @@ def test_attention_kernel_decodes_over_a_context_with_a_far_key(dtype):
     ctx.positions = torch.tensor([n - 1], dtype=torch.int32).cuda()
     ctx.request_of_token = torch.tensor([0], dtype=torch.int32).cuda()
     rt.ops.norm_kv_write(qkv[n - 1:].cuda(), ctx, kv, heads, groups, dim, vdim, ones_q.cuda(), ones_k.cuda(), True, eps, q_out[n - 1:])
-    out = torch.empty(1, heads * vdim, dtype=rt.dtype).cuda()
-    rt.ops.attention_generic(q_out[n - 1:], out, ctx, kv, heads, groups, dim, scale, 0, value_dim=vdim, distance=(r1.cuda(), r2.cuda()))
-    rt.ops.check_errors()
     full = qkv.double()
     q = plain.rms_divide(full[:, :heads * dim], eps).view(n, heads, dim)
     k = plain.rms_divide(full[:, heads * dim:heads * dim + dim], eps).view(n, groups, dim)
     v = plain.rms_divide(full[:, heads * dim + dim:].view(n, groups, vdim), eps)
     want = plain.windowed_softmax_attention(q[n - 1:], k, v, scale, 0, r1.double(), r2.double(), first_position=n - 1)
-    close(out.view(1, heads, vdim), want, dtype, scale=1.0)
+    for few_tokens in (False, True):      # True: the keys are cut into ranges with a CTA each, joined by tickets
+        for _ in range(2):                # twice: the tickets must be back at zero
+            out = torch.zeros(1, heads * vdim, dtype=rt.dtype).cuda()
+            rt.ops.attention_generic(q_out[n - 1:], out, ctx, kv, heads, groups, dim, scale, 0, value_dim=vdim,
+                                     distance=(r1.cuda(), r2.cuda()), few_tokens=few_tokens)
+            rt.ops.check_errors()
+            close(out.view(1, heads, vdim), want, dtype, scale=1.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
