@@ -49,6 +49,7 @@ def zisesun_spec(config: ZisesunConfig) -> ModelSpec:
     layers: list[LayerSpec] = []
     layer_of: dict[int, int] = {}            # config layer -> index into ``layers`` (owners only)
     schedule: list[ScheduleEntry] = []
+    unused: list[str] = []                   # tensors a file may hold for a sublayer the layer does not have
     for index, layer in enumerate(config.layers):
         if layer.weights_of is not None:
             schedule.append(ScheduleEntry(layer=layer_of[layer.weights_of]))
@@ -71,6 +72,8 @@ def zisesun_spec(config: ZisesunConfig) -> ModelSpec:
             if config.streams is not None:
                 parts["feed_forward_connection"] = PartSpec("hyper", dict(streams=config.streams), prefix="hc2.",
                                                             family="connection")
+        else:
+            unused += [f"l{index}.norm2"] + [f"l{index}.hc2.{name}" for name in ("in", "out", "mix")]
         layer_of[index] = len(layers)
         layers.append(LayerSpec(prefix=f"l{index}.", block=PartSpec("stream_residual"), parts=parts))
         schedule.append(ScheduleEntry(layer=layer_of[index]))
@@ -86,6 +89,7 @@ def zisesun_spec(config: ZisesunConfig) -> ModelSpec:
         head_tensor="head",
         max_positions=config.max_positions,
         eos_token_id=None,
+        optional_tensors=tuple(unused),
         position_tensor="pos",
         residual_streams=config.streams or 1,
     )

@@ -73,8 +73,12 @@ CONFIGS = {
     "tiles": config([(attention(heads=4, kv_heads=2, dim=32, vdim=32, window=21, scale=0.3), experts(6, 3, 32)),
                      (lightning(heads=2, dim=16, vdim=48, decay=(0.8, 0.995)), experts(6, 3, 32)),
                      (attention(heads=2, kv_heads=1, dim=64, vdim=64, window=0, scale=0.2), None)], streams=2),
+    # no attention at all: no pages, only state slots
+    "recurrent": config([(lightning(heads=2, dim=16, vdim=16, decay=(0.9, 0.99)), experts(4, 2, 16)),
+                         (lightning(heads=2, dim=16, vdim=16, decay=(0.9, 0.99)), experts(4, 2, 16), 0)],
+                        width=32, vocab=90, streams=2),
 }
-PAGE = {"mixed": 4, "plain": 16, "narrow": 8, "tiles": 16}
+PAGE = {"mixed": 4, "plain": 16, "narrow": 8, "tiles": 16, "recurrent": 8}
 # N(0, 0.02) weights leave the experts, the router and the lightning projections close to nothing
 SCALES = {"mlp.e": 3.0, "mlp.router": 12.0, "mlp.correction": 4.0, "mix.q": 2.0, "mix.k": 2.0, "mix.v": 2.0,
           "embed": 20.0, "pos": 8.0, "head": 6.0}
