@@ -69,7 +69,9 @@ def plan_page_counts(groups: list[GroupSpec], page_size: int, max_requests: int,
     that, and under a byte budget what it does not need goes to the other groups.  ``step_tokens``
     0 means the bound is not known: every group is sized alike."""
     if not groups:
-        return [1]
+        # no layer keeps pages (state slots only): the manager's one empty group still counts tokens in
+        # pages, which cost nothing; give it what was asked for, or no limit under a byte budget
+        return [int(num_pages) if num_pages is not None else 1 << 24]
     caps: list[int | None] = []
     for group in groups:
         if group.window > 0 and step_tokens > 0:

@@ -188,7 +188,8 @@ def test_page_counts_follow_what_a_group_can_use():
     assert plan_page_counts([full, window], 16, max_requests=4, step_tokens=32, num_pages=1000) == [1000, 4 * 7]
     assert plan_page_counts([full, window], 16, max_requests=4, step_tokens=0, num_pages=1000) == [1000, 1000]
     assert plan_page_counts([full], 16, 4, 32, num_pages=77) == [77]
-    assert plan_page_counts([], 16, 4, 32, num_pages=5) == [1]
+    assert plan_page_counts([], 16, 4, 32, num_pages=5) == [5]      # no pages kept: the empty group still counts tokens
+    assert plan_page_counts([], 16, 4, 32, kv_cache_bytes=1 << 20) == [1 << 24]
     # bytes given: equal pages while both grow, then everything to the full group
     budget = 10 * 16 * (1024 + 2048)
     assert plan_page_counts([full, window], 16, 4, 32, kv_cache_bytes=budget) == [10, 10]
