@@ -168,6 +168,60 @@ def test_whole_prompts_decoding_portions_and_batches(folders, name, dtype):
         assert core.cache.free_pages(0) == core.cache.total_pages(0)
 
 
+def drawn_configuration(seed):
+    """A configuration drawn from the whole space of sizes: widths, stream counts, either mixer in any
+    order with head counts, key and value sizes (multiples of 8 and 16 and others, above and below what
+    the chunked and tensor-core kernels take), windows from one key to more than a request has, decays
+    from 0 to 1, experts from one to twelve with any number chosen, layers without feed-forward and
+    layers that run with an earlier layer's tensors."""
+    import random
+
+    rng = random.Random(seed)
+    layers = []
+    for _ in range(rng.randint(1, 5)):
+        if layers and rng.random() < 0.3:
+            owner = rng.randrange(len(layers))
+            layers.append(dict(layers[owner], weights_of=owner))
+            continue
+        if rng.random() < 0.5:
+            kv, group = rng.choice([1, 2, 4]), rng.choice([1, 2, 4, 9])
+            dim = rng.choice([16, 24, 32, 48, 64, 96, 128])
+            vdim = dim if rng.random() < 0.6 else rng.choice([8, 16, 40, 64, 128, 160])
+            mixer = dict(heads=kv * group, kv_heads=kv, dim=dim, vdim=vdim, scale=rng.choice([0.4, 1.2, 4.0]) / dim ** 0.5)
+            if rng.random() < 0.8:
+                mixer["mask"] = {"size": rng.choice([1, 2, 5, 16, 17, 33, 64, 100, 500])}
+            kind = "attention"
+        else:
+            heads = rng.choice([1, 2, 3, 8])
+            mixer = dict(heads=heads, dim=rng.choice([8, 16, 64, 128, 160]), vdim=rng.choice([8, 32, 64, 128, 136]),
+                         decay=[rng.choice([0.0, 0.5, 0.9, 0.99, 0.999, 1.0]) for _ in range(heads)])
+            kind = "lightning"
+        mlp = None
+        if rng.random() < 0.8:
+            count = rng.choice([1, 2, 4, 8, 12])
+            mlp = experts(count, rng.randint(1, count), rng.choice([8, 16, 24, 32, 96, 100]))
+        layers.append(dict(type=kind, mixer=mixer, mlp=mlp))
+    raw = dict(architecture="Zisesun", vocab=rng.choice([50, 211, 448]), width=rng.choice([64, 96, 128, 256]),
+               max_positions=320, norm=dict(eps=rng.choice([1e-6, 1e-5])), layers=layers)
+    streams = rng.choice([None, 1, 2, 2, 3, 4])
+    if streams is not None:
+        raw["streams"] = streams
+    return raw
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_drawn_configurations(seed, tmp_path):
+    raw = drawn_configuration(seed)
+    requests = requests_for(raw, [1, 2, 37, 150], seed=seed)
+    # float32 holds every row to rounding; the bfloat16 run fixes the choice of experts (see SCALES_BF16)
+    for dtype, scales, gate in (("float32", SCALES, 4e-4), ("bfloat16", dict(SCALES_BF16, **{"mlp.correction": 2000.0}), 0.2)):
+        folder = make_model(tmp_path / dtype, raw, 100 + seed, scales=scales)
+        for steps in (trace_whole(requests), trace_mixed(requests, seed=seed, live_limit=3)):
+            pages = -(-peak_tokens(steps, round_to=16) // 16) + 1
+            core = core_for(folder, dtype, 16, pages, slots=3)
+            check(folder, run_trace(core, steps), dtype, gate=gate)
+
+
 def test_float32_rows_do_not_depend_on_the_cut_or_the_batch(folders):
     """The same position through four cuttings: equal to rounding of the order of additions at most."""
     raw = CONFIGS["mixed"]
