@@ -27,9 +27,12 @@ namespace cie {
 using namespace bw;
 using bf16 = __nv_bfloat16;
 
-constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16, STAGES = 3;
-constexpr int A_STAGE_BYTES = BM * BK * 2, B_STAGE_BYTES = BN * BK * 2, STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024;
+constexpr int BM = 128, BK = 64, UMMA_K = 16, STAGES = 3;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+// BN, the output columns of a tile, is 128 (two CTAs an SM) or, on request, 256 (one CTA an SM; a third
+// less operand traffic per product, but nothing beside a tile's set-up and epilogue)
+template <int BN> constexpr int stage_bytes() { return A_STAGE_BYTES + BN * BK * 2; }
+template <int BN> constexpr size_t smem_bytes() { return (size_t)STAGES * stage_bytes<BN>() + 1024; }
 
 __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -65,10 +68,11 @@ struct GroupedArgs {
   int* err;
 };
 
-template <bool kGateUp>
+template <bool kGateUp, int BN>
 __global__ void __launch_bounds__(128) moe_grouped_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                    const __grid_constant__ CUtensorMap map_b,
                                                                    const GroupedArgs a) {
+  constexpr int STAGE_BYTES = stage_bytes<BN>();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* stage_base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -199,18 +203,26 @@ __global__ void __launch_bounds__(128) moe_grouped_tcgen05_kernel(const __grid_c
   if (warp == 0) tmem_free<BN>(tmem_base);
 }
 
-template <bool kGateUp>
+template <bool kGateUp, int BN>
 static int launch_grouped(const CUtensorMap& map_a, const CUtensorMap& map_b, const GroupedArgs& a, dim3 grid,
                           cudaStream_t stream) {
+  constexpr size_t smem = smem_bytes<BN>();
   static bool configured = false;
   if (!configured) {
-    cudaError_t status = cudaFuncSetAttribute(moe_grouped_tcgen05_kernel<kGateUp>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-    if (status != cudaSuccess) CIE_FAIL("moe_tcgen05: shared memory %zu: %s", SMEM_BYTES, cudaGetErrorString(status));
+    cudaError_t status = cudaFuncSetAttribute(moe_grouped_tcgen05_kernel<kGateUp, BN>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (status != cudaSuccess) CIE_FAIL("moe_tcgen05: shared memory %zu: %s", smem, cudaGetErrorString(status));
     configured = true;
   }
-  CIE_LAUNCH("moe_tcgen05", moe_grouped_tcgen05_kernel<kGateUp>, grid, dim3(128), SMEM_BYTES, stream, map_a, map_b, a);
+  CIE_LAUNCH("moe_tcgen05", (moe_grouped_tcgen05_kernel<kGateUp, BN>), grid, dim3(128), smem, stream, map_a, map_b, a);
   return 0;
+}
+
+// 128 columns a tile; CIE_MOE_TILE_COLUMNS=256 asks for the wider tile (measured slower: with one CTA an SM
+// nothing runs beside a tile's set-up and epilogue, 5.63 against 5.41 ms for a 2,048-token prefill)
+static int tile_columns(int) {
+  static const int forced = [] { const char* v = getenv("CIE_MOE_TILE_COLUMNS"); return v ? atoi(v) : 0; }();
+  return forced == 256 ? 256 : 128;
 }
 
 }  // namespace cie
@@ -237,13 +249,15 @@ extern "C" int cie_moe_gate_up_tcgen05(const void* x, void* sorted, const void* 
   if (blocks > 148 * 8) blocks = 148 * 8;
   CIE_LAUNCH("moe_gather_rows", moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, s, (const bf16*)x, (bf16*)sorted,
              place_to_pair, pairs, top, hidden);
+  const int bn = tile_columns(pairs);
   CUtensorMap map_a, map_b;
   if (!tensor_map_bf16(sorted, pairs, hidden, BM, &map_a) ||
-      !tensor_map_bf16(w_gate_up, (long long)experts * 2 * ff, hidden, BN, &map_b))
+      !tensor_map_bf16(w_gate_up, (long long)experts * 2 * ff, hidden, bn, &map_b))
     CIE_FAIL("moe_gate_up_tcgen05: cuTensorMapEncodeTiled failed");
   GroupedArgs a = {act, place_to_pair, tiles, tile_count, 2 * ff, ff, hidden, err};
   const int max_tiles = (pairs + BM - 1) / BM + experts;
-  return launch_grouped<true>(map_a, map_b, a, dim3((2 * ff + BN - 1) / BN, max_tiles), s);
+  const dim3 grid((2 * ff + bn - 1) / bn, max_tiles);
+  return bn == 256 ? launch_grouped<true, 256>(map_a, map_b, a, grid, s) : launch_grouped<true, 128>(map_a, map_b, a, grid, s);
 }
 
 // act: [tokens * top][ff] by place; w_down: [experts][hidden][ff]; rows: float32 [tokens * top][hidden],
@@ -257,11 +271,14 @@ extern "C" int cie_moe_down_tcgen05(const void* act, const void* w_down, float* 
   if ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(w_down) | reinterpret_cast<uintptr_t>(rows)) & 15)
     CIE_FAIL("moe_down_tcgen05: operands must be 16-byte aligned");
   const int pairs = tokens * top;
+  const int bn = tile_columns(pairs);
   CUtensorMap map_a, map_b;
   if (!tensor_map_bf16(act, pairs, ff, BM, &map_a) ||
-      !tensor_map_bf16(w_down, (long long)experts * hidden, ff, BN, &map_b))
+      !tensor_map_bf16(w_down, (long long)experts * hidden, ff, bn, &map_b))
     CIE_FAIL("moe_down_tcgen05: cuTensorMapEncodeTiled failed");
   GroupedArgs a = {rows, place_to_pair, tiles, tile_count, hidden, hidden, ff, err};
   const int max_tiles = (pairs + BM - 1) / BM + experts;
-  return launch_grouped<false>(map_a, map_b, a, dim3((hidden + BN - 1) / BN, max_tiles), (cudaStream_t)stream);
+  const dim3 grid((hidden + bn - 1) / bn, max_tiles);
+  cudaStream_t s = (cudaStream_t)stream;
+  return bn == 256 ? launch_grouped<false, 256>(map_a, map_b, a, grid, s) : launch_grouped<false, 128>(map_a, map_b, a, grid, s);
 }
