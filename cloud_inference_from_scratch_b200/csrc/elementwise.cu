@@ -482,6 +482,33 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
   }
 }
 
+// Gated activation with a capped gate: channel c of a row [gates (inter) | ups (inter)] (plus a bias not
+// yet added, or nullptr) gives  g = min(gate, limit), u = clamp(up, -limit, limit) (limit <= 0: no
+// bounds),  out = g * sigmoid(slope * g) * (u + shift).  The input is float32 or the compute dtype.
+template <typename TI, typename T>
+__global__ void gated_act_kernel(const TI* __restrict__ gate_up, const float* __restrict__ bias, T* __restrict__ out,
+                                 int tokens, int inter, float slope, float limit, float shift) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t total = (size_t)tokens * inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter;
+    const int c = (int)(i % inter);
+    float g = to_float(gate_up[t * 2 * inter + c]);
+    float u = to_float(gate_up[t * 2 * inter + inter + c]);
+    if (bias) {
+      g += bias[c];
+      u += bias[inter + c];
+    }
+    if (limit > 0.f) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+    }
+    out[i] = from_float<T>(g / (1.f + expf(-slope * g)) * (u + shift));
+  }
+}
+
 }  // namespace cie
 
 using namespace cie;
@@ -592,6 +619,26 @@ extern "C" int cie_silu_mul(const void* gate_up, void* out, int tokens, int inte
   DISPATCH_DTYPE(dtype, "silu_mul", {
     CIE_LAUNCH("silu_mul", silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
                (const T*)gate_up, (T*)out, tokens, inter, block);
+  })
+  return 0;
+}
+
+extern "C" int cie_gated_act(const void* gate_up, int in_dtype, const float* bias, void* out, int tokens, int inter,
+                             float slope, float limit, float shift, int dtype, void* stream) {
+  if (tokens <= 0) return 0;
+  const size_t total = (size_t)tokens * inter;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  DISPATCH_DTYPE(dtype, "gated_act", {
+    if (in_dtype == kFloat32) {
+      CIE_LAUNCH("gated_act", (gated_act_kernel<float, T>), dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+                 (const float*)gate_up, bias, (T*)out, tokens, inter, slope, limit, shift);
+    } else if (in_dtype == dtype) {
+      CIE_LAUNCH("gated_act", (gated_act_kernel<T, T>), dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+                 (const T*)gate_up, bias, (T*)out, tokens, inter, slope, limit, shift);
+    } else {
+      CIE_FAIL("gated_act: input type code %d with output type code %d", in_dtype, dtype);
+    }
   })
   return 0;
 }

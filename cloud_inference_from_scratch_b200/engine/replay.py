@@ -29,7 +29,7 @@ import sys
 from pathlib import Path
 
 PAGE_SIZE = 16
-MAX_LIVE_REQUESTS = 8
+MAX_LIVE_REQUESTS = 4      # state slots: a trace holds no more live requests, so slots are used again
 
 
 def parse_args(argv: list[str] | None = None) -> argparse.Namespace:

@@ -24,10 +24,31 @@ class Partials:
 
     def __init__(self, data: Any, splits: int, rows: int, width: int, bias: Any) -> None:
         self.data, self.splits, self.rows, self.width, self.bias = data, splits, rows, width, bias
+        self.stride = rows * width      # elements from one partial sum to the next
 
     @property
     def shape(self) -> tuple[int, int]:
         return (self.rows, self.width)
+
+    @classmethod
+    def of_terms(cls, first: Any, second: Any) -> "Partials":
+        """Two float32 results [rows, width] of equal shape, each contiguous in a buffer of its own,
+        as two terms still to be added: the term at the lower address is the base and the distance
+        between the buffers (in elements) is the stride from one term to the next."""
+        import torch
+
+        if (first.dtype != torch.float32 or second.dtype != torch.float32 or first.shape != second.shape
+                or not first.is_contiguous() or not second.is_contiguous()):
+            raise ValueError("of_terms wants two contiguous float32 tensors of one shape")
+        low, high = (first, second) if first.data_ptr() < second.data_ptr() else (second, first)
+        distance = (high.data_ptr() - low.data_ptr()) // 4
+        rows, width = first.shape
+        if distance < rows * width:
+            raise ValueError("of_terms: the two results overlap")
+        terms = cls(low, 2, rows, width, None)
+        terms.stride = distance
+        terms.terms = (first, second)     # keeps both buffers named for whoever wants to look at them
+        return terms
 
 
 class ResidualSink:

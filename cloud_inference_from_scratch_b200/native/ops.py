@@ -95,6 +95,7 @@ class Ops:
             [v, i, ll, v, v, i, v, v, v, i, i, v, v, v, i, i, i, i, i, i, i, i, i, v, v],
         )
         self._silu_mul = ew.function("cie_silu_mul", [v, v, i, i, i, i, v])
+        self._gated_act = ew.function("cie_gated_act", [v, i, v, v, i, i, f, f, f, i, v])
         gs = _Lib(load_library("gemm_simt.cu"))
         self._gemm_simt = gs.function("cie_gemm_simt", [v, v, v, v, i, i, i, i, i, i, v])
         ag = _Lib(load_library("attention_generic.cu"))
@@ -115,6 +116,8 @@ class Ops:
         # libraries that only some models need are built and loaded when a part first asks for them
         self._streams_lib = None
         self._lightning_lib = None
+        self._latent_lib = None
+        self._delta_lib = None
         self._moe_lib = None
         self._sample = None   # sampling.cu is built when something is first sampled
         self._tensor_gemm = None
@@ -296,7 +299,7 @@ class Ops:
             update = self.resolve(update, None)
         if isinstance(update, Partials):
             self._add_rmsnorm(_ptr(residual), _ptr(update.data), update.splits,
-                              update.rows * update.width, _ptr(update.bias), _ptr(gain), _ptr(out),
+                              update.stride, _ptr(update.bias), _ptr(gain), _ptr(out),
                               _ptr(rows), count, hidden, eps, self._code_of(out), self.stream)
         else:
             self._add_rmsnorm(_ptr(residual), _ptr(update), 0, 0, None, _ptr(gain), _ptr(out),
@@ -433,6 +436,131 @@ class Ops:
         self.launches += 1
         self._lightning_gate_norm(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0), _ptr(gain), _ptr(out),
                                   out.shape[0], out.shape[1], float(eps), self._code_of(out), self.stream)
+
+    # ------------------------------------------------------------------ attention over a cached latent
+    def _load_latent(self) -> None:
+        if self._latent_lib is None:
+            v, i, f = c_void_p, c_int, c_float
+            lib = _Lib(load_library("latent.cu"))
+            self._latent_prepare = lib.function(
+                "cie_latent_prepare", [v, i, v, v, v, v, v, v, i, i, v, v, v, f, i, i, i, i, i, i, i, f, i, i, i, v, v])
+            self._head_linear = lib.function("cie_head_linear", [v, i, i, v, v, i, i, v, i, i, i, i, i, i, i, v])
+            self._latent_attention = lib.function(
+                "cie_latent_attention",
+                [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, v, v])
+            self.latent_max_rank = int(lib.handle.cie_latent_attention_max_rank())
+            self._latent_lib = lib
+
+    def latent_prepare(self, down: Any, q_out: Any, q_gain: Any, kv_gain: Any, ctx: Any, kv: Any, rotation: Any,
+                       q_rank: int, rank: int, rot: int, eps: float, has_kv: bool, write_cache: bool) -> None:
+        """Per token of ``down`` (float32 [T, q_rank (+ rank + rot)]): the query latent divided by its
+        root mean square times ``q_gain`` goes to ``q_out``; with ``has_kv`` and ``write_cache`` the
+        latent, normalised likewise with ``kv_gain``, and the key part, rotated by the token's position,
+        go into the pages (``kv.k``: latents, ``kv.v``: rotated key parts).  ``rotation`` gives
+        ``inv_freq``, ``magnitude``, ``interleaved`` and ``dims``."""
+        self._flush()
+        self._load_latent()
+        table = ctx.block_tables[kv.group]
+        self.launches += 1
+        self._latent_prepare(_ptr(down), down.stride(0), _ptr(q_out), _ptr(q_gain), _ptr(kv_gain), _ptr(ctx.positions),
+                             _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, _ptr(kv.k),
+                             _ptr(kv.v), _ptr(rotation.inv_freq), float(rotation.magnitude), int(rotation.interleaved),
+                             int(rotation.dims), down.shape[0], q_rank, rank, rot, kv.page_size, float(eps),
+                             1 if has_kv else 0, 1 if write_cache else 0, self.code, _ptr(self.error_word), self.stream)
+
+    def head_linear(self, x: Any, x_head: int, weight: Any, out: Any, out_head: int, heads: int, gate: Any = None) -> None:
+        """A product per head: ``out[t, h, :N] = x[t, h, :K] @ weight[h]`` with ``weight`` [heads, K, N] in
+        the compute dtype, ``x`` float32 (head h of a row starts at column ``h * x_head``), ``out`` float32
+        or the compute dtype (head h at column ``h * out_head``); sums in float32, k ascending.  With
+        ``gate`` (float32 [T, heads * N], may be a view of columns) the result is multiplied by sigmoid(gate)."""
+        self._flush()
+        self._load_latent()
+        _, depth, width = weight.shape
+        self.launches += 1
+        self._head_linear(_ptr(x), x.stride(0), x_head, _ptr(weight), _ptr(out), out.stride(0), out_head, _ptr(gate),
+                          gate.stride(0) if gate is not None else 0, x.shape[0], heads, depth, width,
+                          self._code_of(weight), self._code_of(out), self.stream)
+
+    def latent_attention(self, q_latent: Any, q_raw: Any, q_raw_head: int, out: Any, ctx: Any, kv: Any, rotation: Any,
+                         sink: Any, heads: int, rank: int, rot: int, scale: float) -> None:
+        """Causal softmax attention of every (token, head) over the rows [latent | rotated key part] its
+        request holds in the pages: ``q_latent`` float32 [T, heads, rank] meets the latents, the rotated
+        part of ``q_raw`` (float32; head h starts at column ``h * q_raw_head``; rotated here) meets the key
+        parts; ``out`` float32 [T, heads, rank] is the weighted sum of the latents.  ``sink`` (float32
+        [heads] or None) adds exp(sink_h) to the softmax denominator.  With few tokens the keys are cut
+        into ranges over CTAs and joined by a second kernel."""
+        self._flush()
+        self._load_latent()
+        tokens = q_latent.shape[0]
+        table = ctx.block_tables[kv.group]
+        groups = -(-heads // 8)
+        ranges, range_keys, scratch = 1, 1 << 30, None
+        if tokens * groups < self.sm_count:
+            range_keys = 128
+            ranges = max(1, -(-table.shape[1] * kv.page_size // range_keys))
+        if ranges > 1:
+            scratch = self.scratch("latent.ranges", tokens * heads * ranges * (rank + 2))
+        else:
+            ranges, range_keys = 1, 1 << 30
+        self.launches += 2 if ranges > 1 else 1
+        self._latent_attention(_ptr(q_latent), _ptr(q_raw), q_raw.stride(0), q_raw_head, _ptr(out), _ptr(scratch),
+                               _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token), _ptr(table),
+                               table.shape[1], kv.num_pages, _ptr(rotation.inv_freq), float(rotation.magnitude),
+                               int(rotation.interleaved), int(rotation.dims), _ptr(sink), tokens, heads, rank, rot,
+                               kv.page_size, float(scale), range_keys, ranges, self.code, _ptr(self.error_word),
+                               self.stream)
+
+    # ------------------------------------------------------------------ generalized delta rule
+    def _load_delta(self) -> None:
+        if self._delta_lib is None:
+            v, i, f = c_void_p, c_int, c_float
+            lib = _Lib(load_library("delta.cu"))
+            self._tanh_rows = lib.function("cie_tanh_rows", [v, i, v, i, i, i, v])
+            self._delta_scan = lib.function(
+                "cie_delta_scan", [v, i, i, i, i, i, v, i, v, v, v, i, v, v, v, v, i, i, i, i, v, v])
+            self._group_gate_norm = lib.function("cie_group_gate_norm", [v, i, v, i, v, v, i, i, i, i, f, i, v])
+            self.delta_max_dim = int(lib.handle.cie_delta_max_dim())
+            self._delta_lib = lib
+
+    def tanh_rows(self, x: Any, out: Any) -> None:
+        """out = tanh(x) for float32 ``x`` (may be a view of columns), rounded to ``out``'s dtype."""
+        self._flush()
+        self._load_delta()
+        self.launches += 1
+        self._tanh_rows(_ptr(x), x.stride(0), _ptr(out), out.shape[0], out.shape[1], self._code_of(out), self.stream)
+
+    def delta_scan(self, proj: Any, offsets: tuple[int, int, int, int], decay: Any, decay_bias: Any,
+                   removal_bias: Any, out: Any, state: Any, ctx: Any, heads: int, dim: int) -> None:
+        """Runs the generalized delta rule over every request's new tokens from the state in its slot
+        (``state``: float32 [slots, heads, dim, dim]).  ``proj`` float32 rows hold r, k, v and the
+        removal projection from the columns ``offsets``; ``decay`` float32 [T, heads * dim] is the decay
+        projection; both biases are added here; ``out`` float32 [T, heads * dim]."""
+        self._flush()
+        self._load_delta()
+        self.launches += 1
+        r_off, k_off, v_off, a_off = offsets
+        self._delta_scan(_ptr(proj), proj.stride(0), r_off, k_off, v_off, a_off, _ptr(decay), decay.stride(0),
+                         _ptr(decay_bias), _ptr(removal_bias), _ptr(out), out.stride(0), _ptr(state),
+                         _ptr(ctx.query_start), _ptr(ctx.slots), _ptr(ctx.request_active), ctx.num_requests, heads, dim,
+                         state.shape[0], _ptr(self.error_word), self.stream)
+
+    def group_gate_norm(self, o: Any, gate: Any, gain: Any, eps: float, out: Any, groups: int) -> None:
+        """Every group of ``out.shape[1] / groups`` columns of float32 ``o`` divided by its own root mean
+        square, times ``gain`` (all columns), times sigmoid(``gate``) (float32, may be a view of columns)."""
+        self._flush()
+        self._load_delta()
+        self.launches += 1
+        self._group_gate_norm(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0), _ptr(gain), _ptr(out), out.stride(0),
+                              out.shape[0], groups, out.shape[1] // groups, float(eps), self._code_of(out), self.stream)
+
+    def gated_act(self, gate_up: Any, bias: Any, out: Any, slope: float, limit: float, shift: float) -> None:
+        """out[t, c] = g * sigmoid(slope * g) * (u + shift) with g, u the columns c and inter + c of
+        ``gate_up`` (float32 or the compute dtype) plus ``bias`` (or None), g capped at ``limit`` and u
+        clamped to +-``limit`` when ``limit`` > 0."""
+        self._flush()
+        self.launches += 1
+        self._gated_act(_ptr(gate_up), self._code_of(gate_up), _ptr(bias), _ptr(out), out.shape[0], out.shape[1],
+                        float(slope), float(limit), float(shift), self._code_of(out), self.stream)
 
     # ------------------------------------------------------------------ routed experts
     def _load_moe(self) -> None:
@@ -701,6 +829,8 @@ class Ops:
             if value.bias is not None:
                 value.data.add_(value.bias.to(value.data.dtype))
             return value.data
+        if value.stride != value.rows * value.width:
+            raise KernelError("partial sums that lie apart are added up by the norm kernel only")
         total = value.data[: value.splits * value.rows * value.width].view(value.splits, value.rows, value.width).sum(0)
         if value.bias is not None:
             total = total + value.bias

@@ -1,4 +1,4 @@
-from . import attention, block, connection, lightning, mlp, norm, rotary, routed  # noqa: F401  (registers the built-in parts)
+from . import attention, block, connection, delta, latent, lightning, mlp, norm, rotary, routed  # noqa: F401  (registers the built-in parts)
 from .base import (
     Block,
     CacheSpec,

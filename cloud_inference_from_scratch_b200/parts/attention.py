@@ -65,6 +65,8 @@ class Attention(Mixer):
         self.qkv_bias = bool(qkv_bias)
         self.window = int(window)
         self.position = build_part("position", position) if position is not None else None
+        if getattr(self.position, "magnitude", 1.0) != 1.0 or getattr(self.position, "keep_pairing", False):
+            raise ValueError("this mixer's kernels rotate without a magnitude factor and pair (j, j + R/2) only")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.scale *= float(getattr(self.position, "attention_factor", 1.0))
         self.q_width = self.num_heads * self.head_dim

@@ -79,3 +79,31 @@ class StreamResidual(Block):
 
 
 register_part("block", "stream_residual", StreamResidual, replace=True)
+
+
+class ParallelResidual(Block):
+    """One norm, and both sublayers read its output: ``x <- x + (mixer(h) + feed_forward(h))`` with
+    ``h = norm(x)``; a layer without a feed-forward is ``x <- x + mixer(h)``.  Both results are float32
+    and stay apart: they travel to the next norm as a ``Partials`` of two terms, whose kernel adds
+    them up and into the stream in float32."""
+
+    slots = ("mixer", "mixer_norm")
+
+    def forward(self, residual, pending, ctx, binding):
+        from ..lazy import Partials
+
+        sink = getattr(ctx, "residual_sink", None)
+        if sink is not None:
+            ctx.residual_sink = None      # nothing of this block adds itself into the stream
+        x = self.mixer_norm.forward(residual, pending, ctx)
+        mixed = self.mixer.forward(x, ctx, binding)
+        feed_forward = self.parts.get("feed_forward")
+        if feed_forward is None:
+            result = Partials(mixed, 1, mixed.shape[0], mixed.shape[1], None)
+        else:
+            result = Partials.of_terms(mixed, feed_forward.forward(x, ctx))
+        ctx.residual_sink = sink
+        return result
+
+
+register_part("block", "parallel_residual", ParallelResidual, replace=True)

@@ -42,3 +42,52 @@ class SwiGLU(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+
+
+class ClampedGLU(FeedForward):
+    """Gated feed-forward with biases, a capped gate and a shifted up branch:
+    ``g = min(W_gate x + b_gate, limit)``, ``u = clamp(W_up x + b_up, -limit, limit)``,
+    ``y = g * sigmoid(slope * g) * (u + shift)``, result ``W_down y + b_down``.  Gate and up are one
+    stacked product with float32 results; biases, bounds and activation run in float32 in one kernel.
+    The result is float32 (a term of the residual sum).  Tensor names: ``gate``, ``gate.b``, ``up``,
+    ``up.b``, ``down``, ``down.b``."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, slope: float = 1.702,
+                 shift: float = 1.0) -> None:
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.limit = float(limit)
+        self.slope = float(slope)
+        self.shift = float(shift)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        inter, hidden = self.intermediate_size, self.hidden_size
+        return {
+            "gate": TensorSpec((inter, hidden)), "gate.b": TensorSpec((inter,), role="vector"),
+            "up": TensorSpec((inter, hidden)), "up.b": TensorSpec((inter,), role="vector"),
+            "down": TensorSpec((hidden, inter)), "down.b": TensorSpec((hidden,), role="vector"),
+        }
+
+    def bind(self, tensors, runtime) -> None:
+        import torch
+
+        self.runtime = runtime
+        self.w_gate_up = runtime.ops.prepare_weight(torch.cat([tensors["gate"], tensors["up"]]))
+        self.b_gate_up = torch.cat([tensors["gate.b"], tensors["up.b"]]).contiguous()
+        self.w_down = runtime.ops.prepare_weight(tensors["down"])
+        self.b_down = tensors["down.b"].contiguous()
+
+    def forward(self, x, ctx):
+        import torch
+
+        rt = self.runtime
+        tokens = x.shape[0]
+        both = rt.workspace.get("glu.gate_up", tokens, 2 * self.intermediate_size, torch.float32)
+        rt.ops.linear(x, self.w_gate_up, None, both)
+        hidden = rt.workspace.get("glu.hidden", tokens, self.intermediate_size, rt.dtype)
+        rt.ops.gated_act(both, self.b_gate_up, hidden, self.slope, self.limit, self.shift)
+        update = rt.workspace.get("feed_forward.update32", tokens, self.hidden_size, torch.float32)
+        return rt.ops.linear(hidden, self.w_down, self.b_down, update)
+
+
+register_part("feed_forward", "clamped_glu", ClampedGLU, replace=True)

@@ -13,16 +13,24 @@ from .base import Norm, TensorSpec, register_part
 
 
 class RMSNorm(Norm):
-    def __init__(self, hidden_size: int, eps: float) -> None:
+    """``gain_offset``: the stored vector w lies around zero and the gain is ``gain_offset + w`` (formed
+    once, in float32, when the tensors are bound).  ``name``: the tensor's name after the part's prefix."""
+
+    def __init__(self, hidden_size: int, eps: float, gain_offset: float = 0.0, name: str = "weight") -> None:
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)
+        self.gain_offset = float(gain_offset)
+        self.name = str(name)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.hidden_size,), init="gain", role="vector")}
+        init = "gain" if self.gain_offset == 0.0 else "normal"
+        return {self.name: TensorSpec((self.hidden_size,), init=init, role="vector")}
 
     def bind(self, tensors, runtime) -> None:
         self.runtime = runtime
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.name]
+        if self.gain_offset != 0.0:
+            self.weight = (self.weight.float() + self.gain_offset).contiguous()
 
     accepts_accumulated = True   # ``update`` may be an ``Accumulated``: the sum is already in the stream
     kernels_through_ops = True  # every kernel of this part is a method of ``Ops``: a decode step may be recorded

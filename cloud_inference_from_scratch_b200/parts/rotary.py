@@ -17,9 +17,20 @@ Beyond the reference (which has exactly the above):
   reads q or k.
 * ``position_scale`` divides positions (linear position scaling); ``attention_factor`` multiplies
   the softmax scale of the mixer that owns this encoding.
+* ``ramp`` = (factor, original, fast, slow) blends every frequency f_i between itself and
+  f_i / factor: with ``d(t) = R ln(original / (2 pi t)) / (2 ln theta)`` (the pair index at which
+  ``original`` positions make ``t`` turns), ``lo = max(floor(d(fast)), 0)``, ``hi = min(ceil(d(slow)),
+  R - 1)`` and ``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the frequency is
+  ``f_i / factor * r_i + f_i * (1 - r_i)``; cos and sin are then both multiplied by
+  ``magnitude = 0.1 ln(factor) + 1`` (a mixer that rotates with kernels of its own reads
+  ``magnitude``; the softmax scale is left alone).
+* ``keep_pairing``: ``row_order`` answers None although the pairing is interleaved, for a mixer whose
+  kernels rotate either pairing themselves (``pairing`` tells them which).
 """
 
 from __future__ import annotations
+
+import math
 
 from .base import PositionEncoding, register_part
 
@@ -28,7 +39,8 @@ class RopeNeox(PositionEncoding):
     style = "neox"
 
     def __init__(self, head_dim: int, rotary_dim: int, theta: float, max_positions: int,
-                 pairing: str = "half", position_scale: float = 1.0, attention_factor: float = 1.0) -> None:
+                 pairing: str = "half", position_scale: float = 1.0, attention_factor: float = 1.0,
+                 ramp: tuple[float, float, float, float] | None = None, keep_pairing: bool = False) -> None:
         if rotary_dim % 2 or rotary_dim > head_dim or rotary_dim < 2:
             raise ValueError(f"rotary_dim {rotary_dim} must be even and within head_dim {head_dim}")
         if pairing not in ("half", "interleaved"):
@@ -42,11 +54,33 @@ class RopeNeox(PositionEncoding):
         self.pairing = pairing
         self.position_scale = float(position_scale)
         self.attention_factor = float(attention_factor)
+        self.ramp = tuple(float(value) for value in ramp) if ramp is not None else None
+        if self.ramp is not None and (len(self.ramp) != 4 or min(self.ramp) <= 0):
+            raise ValueError("ramp must be (factor, original, fast, slow), all positive")
+        self.magnitude = 0.1 * math.log(self.ramp[0]) + 1.0 if self.ramp is not None else 1.0
+        self.keep_pairing = bool(keep_pairing)
+
+    def frequencies(self) -> list[float]:
+        """f_i for i < rotary_dim / 2, in double precision."""
+        dims, half = self.rotary_dim, self.rotary_dim // 2
+        plain = [self.theta ** (-2.0 * i / dims) / self.position_scale for i in range(half)]
+        if self.ramp is None:
+            return plain
+        factor, original, fast, slow = self.ramp
+
+        def pair_index(turns: float) -> float:
+            return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(pair_index(fast)), 0)
+        hi = min(math.ceil(pair_index(slow)), dims - 1)
+        width = max(hi - lo, 0.001)
+        blend = [min(max((i - lo) / width, 0.0), 1.0) for i in range(half)]
+        return [f / factor * r + f * (1.0 - r) for f, r in zip(plain, blend)]
 
     def row_order(self) -> list[int] | None:
         """For a mixer: the order in which the elements of a q or k head are to be stored so that
         this encoding's pairs are (j, j + rotary_dim/2) for the kernels; None if they are already."""
-        if self.pairing == "half":
+        if self.pairing == "half" or self.keep_pairing:
             return None
         half = self.rotary_dim // 2
         order = [2 * j for j in range(half)] + [2 * j + 1 for j in range(half)]
@@ -56,8 +90,11 @@ class RopeNeox(PositionEncoding):
         import torch
 
         self.runtime = runtime
-        exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
-        inv_freq = 1.0 / (self.theta ** exponent) / self.position_scale
+        if self.ramp is None:
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+            inv_freq = 1.0 / (self.theta ** exponent) / self.position_scale
+        else:
+            inv_freq = torch.tensor(self.frequencies(), dtype=torch.float64).to(torch.float32)
         self.inv_freq = inv_freq.to(runtime.device).contiguous()
 
 

@@ -99,6 +99,9 @@ class RandomSource:
         import torch
 
         spec = self.table[name]
+        if any(size < 0 for size in spec.shape):
+            raise WeightsError(f"tensor {name}: the model description leaves a size open ({list(spec.shape)}); "
+                               "random weights need it named in the configuration")
         generator = torch.Generator(device=self.device)
         generator.manual_seed(_tensor_seed(self.seed, name))
         if spec.init == "zeros":
