@@ -186,3 +186,35 @@ def forward(config: dict, tensors: dict, tokens: list[int], layer_outputs: list 
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
     return offset_gain_norm(x, t["final.norm"], eps) @ t["head"].T
+
+
+def first_token_delta_margin(config: dict, tensors: dict, tokens: list[int]) -> float:
+    """At a request's first token a head of the delta rule puts out (k . r) v, and the head norm
+    that follows keeps only the SIGN of k . r.  Returns the smallest |cos(k, r)| over all such heads:
+    where it is nearly zero, rounding decides that sign and the row is no measure of anything."""
+    t = {name: value.to(F) for name, value in tensors.items()}
+    outputs: list = []
+    forward(config, tensors, tokens[:1], outputs)
+    inputs = [t["embed"][torch.tensor(tokens[:1], dtype=torch.long)]] + outputs
+    margin = 1.0
+    for index, layer in enumerate(config["layers"]):
+        if layer["type"] != "general_delta":
+            continue
+        heads, dim = layer["mixer"]["heads"], layer["mixer"]["dim"]
+        h = offset_gain_norm(inputs[index], t[f"l{index}.norm1"], config["norm"]["eps"])
+        r = (h @ t[f"l{index}.mix.r"].T).view(heads, dim)
+        k = (h @ t[f"l{index}.mix.k"].T).view(heads, dim)
+        cosine = (r * k).sum(-1) / (r.norm(dim=-1) * k.norm(dim=-1))
+        margin = min(margin, float(cosine.abs().min()))
+    return margin
+
+
+def read_folder(folder):
+    """config.json and the tensors of a model folder."""
+    import json
+    from pathlib import Path
+
+    import safetensors.torch
+
+    config = json.loads((Path(folder) / "config.json").read_text())
+    return config, safetensors.torch.load_file(str(Path(folder) / "model.safetensors"))
