@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl own|reference]
-                    [--config 3b|7b-mixed|14b-pressure|zisesun] [--quick]
+                    [--config 3b|7b-mixed|14b-pressure|zisesun|lodalix] [--quick]
 
 Prints ONE JSON line.  The default configuration is the Qwen2.5-3B shape: a "step" is one decode
 step of a batch of requests whose prompts (2,048 random tokens each) were prefilled before;
@@ -26,6 +26,11 @@ of 256 and 512 tokens, and (unless ``--quick``) the two other benchmark configur
   layers, beside the Qwen2 dense shape of equal width, layer count, head sizes and active
   feed-forward size: a 2,048-token prompt in one step, and decode steps of 8 requests at that
   context, both through the step function.
+
+* ``lodalix``: the Lodalix design (latent attention with a sink or with an output gate and ramped
+  rotary frequencies, layers that read an earlier layer's latent, the generalized delta rule, a
+  clamped gated feed-forward beside the mixer) at two sizes, beside the Qwen2 dense shape of equal
+  width, layer count, head count and feed-forward size, measured the same way.
 
 ``check`` compares, at the full 36 layers, the logits of the bfloat16 generation path with the
 32-bit path of the same weights (``engine/check.py``).  ``--config`` prints the line of one of the
@@ -578,6 +583,35 @@ ZISESUN_SIZES = {
 }
 
 
+def _lodalix(width, layers, heads, dim, rot_dim, vdim, kv_rank, q_rank, delta_heads, delta_dim, ff, vocab=32000) -> dict:
+    """Layers in the order: latent attention with a sink, latent attention with a gate, the same reading
+    the latent of the layer before it, the delta rule; and again."""
+    scale = (dim + rot_dim) ** -0.5
+    first = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, scale=scale,
+                 rot=dict(base=10000.0, dims=rot_dim))
+    second = dict(first, rot=dict(base=10000.0, dims=rot_dim, scaling=dict(factor=4.0, original=1024, fast=32.0, slow=1.0)))
+    mlp = dict(kind="dense", ff=ff, limit=7.0)
+    entries = []
+    for index in range(layers):
+        turn = index % 4
+        if turn == 0:
+            entries.append(dict(type="latent_attention", mixer=first, mlp=mlp))
+        elif turn == 1:
+            entries.append(dict(type="latent_attention_2", mixer=second, mlp=mlp))
+        elif turn == 2:
+            entries.append(dict(type="latent_attention_2", mixer=dict(second, kv_from=index - 1), mlp=mlp))
+        else:
+            entries.append(dict(type="general_delta", mixer=dict(heads=delta_heads, dim=delta_dim, decay_rank=64), mlp=mlp))
+    return dict(architecture="Lodalix", vocab=vocab, width=width, norm=dict(eps=1e-6), layers=entries)
+
+
+# (Lodalix configuration, the Qwen2 dense shape of equal width, layers, heads and feed-forward size)
+LODALIX_SIZES = {
+    "w2048": (_lodalix(2048, 8, 16, 128, 64, 128, 512, 768, 32, 64, 5504), dict(_qwen2(2048, 8, 16, 2, 5504, 32000, False))),
+    "w4096": (_lodalix(4096, 4, 32, 128, 64, 128, 512, 1536, 64, 64, 8192), dict(_qwen2(4096, 4, 32, 8, 8192, 32000, False))),
+}
+
+
 def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int, only: str = "all") -> dict:
     """Prefill of one PROMPT_TOKENS prompt in one step (median of 5 after 3), then ``steps`` decode
     steps of ``batch`` requests that each hold a PROMPT_TOKENS context, through the step function;
@@ -645,8 +679,11 @@ def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int, only: st
                 decode_tokens_per_s=round(batch / decode_ms * 1e3, 1), decode_launches=decode_launches)
 
 
-def run_zisesun(args: argparse.Namespace) -> int:
+def run_zisesun(args: argparse.Namespace, design: str = "zisesun") -> int:
     import torch
+
+    sizes = {"zisesun": ZISESUN_SIZES, "lodalix": LODALIX_SIZES}[design]
+    title = design.capitalize()
 
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device; this engine has no CPU path"}))
@@ -654,26 +691,26 @@ def run_zisesun(args: argparse.Namespace) -> int:
     sampler = ClockSampler()
     sampler.start()
     points = {}
-    for name, (zisesun, qwen) in ZISESUN_SIZES.items():
+    for name, (zisesun, qwen) in sizes.items():
         if args.size not in ("all", name):
             continue
         if args.layers:
             zisesun = dict(zisesun, layers=zisesun["layers"][:args.layers])
             qwen = dict(qwen, num_hidden_layers=args.layers)
         points[name] = {}
-        if args.model in ("both", "zisesun"):
-            points[name]["zisesun"] = _time_step_function(zisesun, args.batch, args.steps, args.warmup, args.only)
+        if args.model in ("both", design):
+            points[name][design] = _time_step_function(zisesun, args.batch, args.steps, args.warmup, args.only)
         if args.model in ("both", "qwen2"):
             points[name]["qwen2_dense"] = _time_step_function(qwen, args.batch, args.steps, args.warmup, args.only)
         points[name]["layers"] = len(zisesun["layers"])
     first = next(iter(points.values()))
-    main = first.get("zisesun") or first["qwen2_dense"]
-    line = {"metric": "decode tok/s, Zisesun design at width 2,048 (8 requests at context 2,048), step function",
+    main = first.get(design) or first["qwen2_dense"]
+    line = {"metric": f"decode tok/s, {title} design at width 2,048 (8 requests at context 2,048), step function",
             "value": main["decode_tokens_per_s"], "unit": "tokens/s", "higher_is_better": True,
             "ms_per_step": main["decode_ms_per_step"], "steps": args.steps, "n_gpus": 1, "warmup": args.warmup,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "own",
             "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
-            "config": {"model": "Zisesun sizes beside Qwen2 dense shapes of equal width, layers, heads and active "
+            "config": {"model": f"{title} sizes beside Qwen2 dense shapes of equal width, layers, heads and active "
                                 "feed-forward size", "global_batch": args.batch, "seq_len": PROMPT_TOKENS,
                        "page_size": PAGE, "parallelism": "single GPU", "inputs_larger_than_l2": True},
             "points": points, "peaks": peaks(), "clocks": sampler.stop()}
@@ -713,10 +750,10 @@ def main() -> int:
                         help="prompt length of every request and of the timed prefill (the record's "
                              "default is 2048; longer ones are for profiles of long contexts, own arm only)")
     parser.add_argument("--impl", default="own", choices=("own", "reference"))
-    parser.add_argument("--size", default="all", help="--config zisesun: one of its sizes (w2048, w4096)")
-    parser.add_argument("--model", default="both", choices=("both", "zisesun", "qwen2"),
-                        help="--config zisesun: only the new design, or only its dense peer")
-    parser.add_argument("--config", default="3b", choices=("3b", "7b-mixed", "14b-pressure", "zisesun"),
+    parser.add_argument("--size", default="all", help="--config zisesun or lodalix: one of its sizes (w2048, w4096)")
+    parser.add_argument("--model", default="both", choices=("both", "zisesun", "lodalix", "qwen2"),
+                        help="--config zisesun or lodalix: only the new design, or only its dense peer")
+    parser.add_argument("--config", default="3b", choices=("3b", "7b-mixed", "14b-pressure", "zisesun", "lodalix"),
                         help="the benchmark configuration whose line is printed (default: the 3B line, "
                              "which also carries the other two as points)")
     parser.add_argument("--quick", action="store_true",
@@ -740,8 +777,8 @@ def main() -> int:
         CONTEXT = min(limit, PROMPT_TOKENS + max(2048, room))
     if args.impl == "reference":
         return run_reference(args)
-    if args.config == "zisesun":
-        return run_zisesun(args)
+    if args.config in ("zisesun", "lodalix"):
+        return run_zisesun(args, args.config)
     if args.config != "3b":
         return run_other_config(args)
     return run_own(args)

@@ -352,6 +352,15 @@ extern "C" int cie_head_linear(const float* x, int x_stride, int x_head, const v
   return 0;
 }
 
+extern "C" int cie_latent_merge(const float* part, float* out, const int* positions, const float* sink, int tokens,
+                                int heads, int rank, int range_keys, int ranges, void* stream) {
+  using namespace cie;
+  if (tokens <= 0) return 0;
+  CIE_LAUNCH("latent_merge", latent_merge_kernel, dim3(tokens, heads), dim3(128), 0, (cudaStream_t)stream, part, out,
+             positions, sink, heads, rank, range_keys, ranges);
+  return 0;
+}
+
 extern "C" int cie_latent_attention_max_rank() { return 512; }
 
 extern "C" int cie_latent_attention(const float* q_abs, const float* q_raw, int q_raw_stride, int q_raw_head,

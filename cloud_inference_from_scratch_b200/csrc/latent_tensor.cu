@@ -1,0 +1,372 @@
+// Attention over cached latent rows on the tensor cores (bfloat16 pages; see latent.cu for the
+// arithmetic and the plain kernel that serves every other case).
+//
+// One CTA per (token, group of 16 heads, key range): the 16 heads of a token are the 16 rows of an
+// mma.sync tile, since all heads of a token read the same rows [c_j | kr_j].  Keys come 64 at a time
+// into shared memory with cp.async (two buffers: tile i+1 is on its way while tile i is used) and
+// serve twice, as the key operand of the scores and, their first `rank` columns, as the value
+// operand of the sums.  Eight warps: for the scores warp w takes keys 8w .. 8w+7 of the tile over
+// all of [rank + rot]; for the sums warp w takes latent columns w * CW .. (w + 1) * CW - 1 over all 64
+// keys.  Between the two the softmax weights pass through shared memory as TWO bfloat16 terms
+// (the weight rounded, and what the rounding left), so that 16 bits of a float32 weight's mantissa
+// reach the sum; maxima, sums and the denominators are float32, and the query is rounded to
+// bfloat16 once, after its plain part was carried into the latent space in float32.
+//
+// ranges == 1: the normalised sum (with the sink term, if any, in the denominator) goes to `out`
+// [T, heads, rank]; else the CTA leaves (maximum, sum, unnormalised latent sum) in `part`
+// [T, heads, ranges, rank + 2] for latent_merge (latent.cu), as the plain kernel does.
+#include "common.cuh"
+
+#include <cfloat>
+
+CIE_DEFINE_LAST_ERROR()
+
+namespace cie {
+
+using bf16 = __nv_bfloat16;
+constexpr int kWarps = 8;
+constexpr int kRows = 16;        // heads of a CTA
+constexpr int kTile = 64;        // keys of a tile
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t& r0, uint32_t& r1, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t& r0, uint32_t& r1, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+struct Layout {
+  int depth;      // rank + rot rounded up to 16: the K extent of the scores
+  int ld;         // elements of a shared-memory row: covers depth and 8 * column_width, plus 8 (an odd number of 16-byte units)
+  __host__ __device__ static Layout of(int rank, int rot, int column_width) {
+    Layout l;
+    l.depth = (rank + rot + 15) / 16 * 16;
+    const int widest = l.depth > kWarps * column_width ? l.depth : kWarps * column_width;
+    l.ld = widest + 8;
+    return l;
+  }
+  __host__ __device__ size_t bytes() const {
+    return ((size_t)(kRows + 2 * kTile) * ld + 2 * kRows * (kTile + 8)) * sizeof(bf16) +
+           (size_t)(2 * kWarps * kRows) * sizeof(float) + 2 * kTile * sizeof(long long);
+  }
+};
+
+// NT: 8-column tiles of the latent a warp sums (column width CW = 8 * NT; 8 warps cover rank <= 64 * NT).
+template <int NT>
+__global__ void __launch_bounds__(kWarps * 32)
+latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __restrict__ q_raw, int q_raw_stride,
+                               int q_raw_head, float* __restrict__ out, float* __restrict__ part,
+                               const bf16* __restrict__ c_pool, const bf16* __restrict__ r_pool,
+                               const int* __restrict__ positions, const int* __restrict__ request_of_token,
+                               const int* __restrict__ table, int table_width, int num_pages,
+                               const float* __restrict__ inv_freq, float magnitude, int interleaved, int rot_dims,
+                               const float* __restrict__ sink, int heads, int rank, int rot, int page_size, float scale,
+                               int range_keys, int ranges, int* err) {
+  extern __shared__ __align__(16) unsigned char shared_raw[];
+  constexpr int CW = 8 * NT;
+  const Layout lay = Layout::of(rank, rot, CW);
+  const int ld = lay.ld;
+  bf16* qs = reinterpret_cast<bf16*>(shared_raw);                 // [16][ld]
+  bf16* ks = qs + kRows * ld;                                      // [2][64][ld]
+  bf16* ps = ks + 2 * kTile * ld;                                  // [2 terms][16][64 + 8]
+  float* wmax = reinterpret_cast<float*>(ps + 2 * kRows * (kTile + 8));   // [8 warps][16]
+  float* wsum = wmax + kWarps * kRows;                             // [8 warps][16]
+  long long* row_of = reinterpret_cast<long long*>(wsum + kWarps * kRows);   // [2][64]
+  constexpr int PLD = kTile + 8;
+
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int h0 = blockIdx.y * kRows;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, tg = lane & 3;
+  const int pos = positions[t];
+  const int length = pos + 1;
+  const int begin = blockIdx.z * range_keys;
+  if (begin >= length) return;
+  const int end = min(length, begin + range_keys);
+  const int* pages = table + (size_t)request_of_token[t] * table_width;
+  const int D = rank + rot;
+
+  // everything starts as zero: padding columns and rows that no copy writes must not hold NaN patterns
+  {
+    uint4* words = reinterpret_cast<uint4*>(shared_raw);
+    const int count = (int)(((size_t)(kRows + 2 * kTile) * ld + 2 * kRows * PLD) * sizeof(bf16) / 16);
+    for (int i = tid; i < count; i += blockDim.x) words[i] = make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+
+  // the query rows: the latent part as it comes, the rotated part rotated here, both rounded once
+  for (int e = tid; e < kRows * rank; e += blockDim.x) {
+    const int r = e / rank, d = e % rank;
+    if (h0 + r < heads) qs[r * ld + d] = __float2bfloat16_rn(q_abs[((size_t)t * heads + h0 + r) * rank + d]);
+  }
+  for (int e = tid; e < kRows * (rot_dims / 2); e += blockDim.x) {
+    const int r = e / (rot_dims / 2), i = e % (rot_dims / 2);
+    if (h0 + r >= heads) continue;
+    const float* qr = q_raw + (size_t)t * q_raw_stride + (size_t)(h0 + r) * q_raw_head;
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + rot_dims / 2;
+    float s, c;
+    sincosf((float)pos * inv_freq[i], &s, &c);
+    s *= magnitude;
+    c *= magnitude;
+    const float u = qr[a], v = qr[b];
+    qs[r * ld + rank + a] = __float2bfloat16_rn(u * c - v * s);
+    qs[r * ld + rank + b] = __float2bfloat16_rn(v * c + u * s);
+  }
+  for (int e = tid; e < kRows * (rot - rot_dims); e += blockDim.x) {
+    const int r = e / (rot - rot_dims), i = rot_dims + e % (rot - rot_dims);
+    if (h0 + r < heads)
+      qs[r * ld + rank + i] = __float2bfloat16_rn(q_raw[(size_t)t * q_raw_stride + (size_t)(h0 + r) * q_raw_head + i]);
+  }
+
+  const int chunks = D / 8;                 // 16-byte pieces of a row [c | kr] (rank and rot are multiples of 8)
+  const int rank_chunks = rank / 8;
+  auto fetch = [&](int base, int buf) {
+    // which row of the pools every key of the tile lives in
+    if (tid < kTile) {
+      long long r = -1;
+      const int key = base + tid;
+      if (key < end) {
+        const int page = pages[key / page_size];
+        if (page < 0 || page >= num_pages) atomicOr(err, kErrBadPage);
+        else r = (long long)page * page_size + key % page_size;
+      }
+      row_of[buf * kTile + tid] = r;
+    }
+  };
+  auto copy = [&](int buf) {
+    bf16* dst = ks + (size_t)buf * kTile * ld;
+    for (int e = tid; e < kTile * chunks; e += blockDim.x) {
+      const int j = e / chunks, c = e % chunks;
+      const long long r = row_of[buf * kTile + j];
+      const bool valid = r >= 0;
+      const bf16* src = c < rank_chunks ? c_pool + (valid ? (size_t)r * rank + c * 8 : 0)
+                                        : r_pool + (valid ? (size_t)r * rot + (c - rank_chunks) * 8 : 0);
+      cp_async16(dst + j * ld + c * 8, src, valid);
+    }
+    cp_async_commit();
+  };
+
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -FLT_MAX, m1 = -FLT_MAX;     // running maxima of rows g and g + 8 (the same in every warp)
+  float l0 = 0.f, l1 = 0.f;               // this thread's share of the rows' sums (its own keys only)
+
+  const int tiles = (end - begin + kTile - 1) / kTile;
+  fetch(begin, 0);
+  __syncthreads();
+  copy(0);
+  for (int i = 0; i < tiles; ++i) {
+    const int buf = i & 1;
+    const int base = begin + i * kTile;
+    if (i + 1 < tiles) fetch(base + kTile, buf ^ 1);
+    cp_async_wait<0>();
+    __syncthreads();          // [A] tile i has landed; everybody is done with tile i - 1, the weights and the maxima
+    if (i + 1 < tiles) copy(buf ^ 1);
+    const bf16* kt = ks + (size_t)buf * kTile * ld;
+
+    // scores of keys 8 * warp .. + 7 for the 16 rows
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const bf16* a_ptr = qs + (lane & 15) * ld + (lane >> 4) * 8;
+      const bf16* b_ptr = kt + (warp * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8;
+      for (int k0 = 0; k0 < lay.depth; k0 += 16) {
+        uint32_t a[4], b0, b1;
+        ldsm_x4(a, a_ptr + k0);
+        ldsm_x2(b0, b1, b_ptr + k0);
+        mma_bf16(s, a, b0, b1);
+      }
+    }
+    const int key0 = base + warp * 8 + 2 * tg;
+    const bool in0 = key0 < end, in1 = key0 + 1 < end;
+    s[0] = in0 ? s[0] * scale : -FLT_MAX;
+    s[1] = in1 ? s[1] * scale : -FLT_MAX;
+    s[2] = in0 ? s[2] * scale : -FLT_MAX;
+    s[3] = in1 ? s[3] * scale : -FLT_MAX;
+    const float top0 = quad_max(fmaxf(s[0], s[1])), top1 = quad_max(fmaxf(s[2], s[3]));
+    if (tg == 0) {
+      wmax[warp * kRows + g] = top0;
+      wmax[warp * kRows + g + 8] = top1;
+    }
+    __syncthreads();          // [B]
+    float new0 = m0, new1 = m1;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      new0 = fmaxf(new0, wmax[w * kRows + g]);
+      new1 = fmaxf(new1, wmax[w * kRows + g + 8]);
+    }
+    const float fix0 = expf(m0 - new0), fix1 = expf(m1 - new1);
+    m0 = new0;
+    m1 = new1;
+    const float p0 = in0 ? expf(s[0] - m0) : 0.f, p1 = in1 ? expf(s[1] - m0) : 0.f;
+    const float p2 = in0 ? expf(s[2] - m1) : 0.f, p3 = in1 ? expf(s[3] - m1) : 0.f;
+    l0 = l0 * fix0 + p0 + p1;
+    l1 = l1 * fix1 + p2 + p3;
+    {
+      // the weight as two bfloat16 terms: its rounding, and the rounding of what that left
+      const __nv_bfloat162 hi_a = __floats2bfloat162_rn(p0, p1), hi_b = __floats2bfloat162_rn(p2, p3);
+      const float2 fa = __bfloat1622float2(hi_a), fb = __bfloat1622float2(hi_b);
+      const __nv_bfloat162 lo_a = __floats2bfloat162_rn(p0 - fa.x, p1 - fa.y), lo_b = __floats2bfloat162_rn(p2 - fb.x, p3 - fb.y);
+      const int col = warp * 8 + 2 * tg;
+      *reinterpret_cast<__nv_bfloat162*>(ps + g * PLD + col) = hi_a;
+      *reinterpret_cast<__nv_bfloat162*>(ps + (g + 8) * PLD + col) = hi_b;
+      *reinterpret_cast<__nv_bfloat162*>(ps + kRows * PLD + g * PLD + col) = lo_a;
+      *reinterpret_cast<__nv_bfloat162*>(ps + kRows * PLD + (g + 8) * PLD + col) = lo_b;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o[n][0] *= fix0;
+      o[n][1] *= fix0;
+      o[n][2] *= fix1;
+      o[n][3] *= fix1;
+    }
+    __syncthreads();          // [C] all weights of the tile are in shared memory
+    {
+      const bf16* a_ptr = ps + (lane & 15) * PLD + (lane >> 4) * 8;
+      const bf16* b_ptr = kt + (lane & 15) * ld + warp * CW;
+#pragma unroll
+      for (int k0 = 0; k0 < kTile; k0 += 16) {
+        uint32_t hi[4], lo[4];
+        ldsm_x4(hi, a_ptr + k0);
+        ldsm_x4(lo, a_ptr + kRows * PLD + k0);
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          uint32_t b0, b1;
+          ldsm_x2_trans(b0, b1, b_ptr + k0 * ld + n * 8);
+          mma_bf16(o[n], hi, b0, b1);
+          mma_bf16(o[n], lo, b0, b1);
+        }
+      }
+    }
+  }
+
+  // the rows' sums: over the four threads of a quad, then over the warps
+  l0 = quad_sum(l0);
+  l1 = quad_sum(l1);
+  __syncthreads();
+  if (tg == 0) {
+    wsum[warp * kRows + g] = l0;
+    wsum[warp * kRows + g + 8] = l1;
+  }
+  __syncthreads();
+  float total0 = 0.f, total1 = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    total0 += wsum[w * kRows + g];
+    total1 += wsum[w * kRows + g + 8];
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int h = h0 + g + 8 * half;
+    if (h >= heads) continue;
+    const float m = half ? m1 : m0, l = half ? total1 : total0;
+    if (ranges == 1) {
+      float total = l, keep = 1.f;
+      if (sink) {
+        const float top = fmaxf(m, sink[h]);
+        keep = expf(m - top);
+        total = l * keep + expf(sink[h] - top);
+      }
+      const float inv = keep / total;
+      float* dst = out + ((size_t)t * heads + h) * rank;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int col = warp * CW + n * 8 + 2 * tg;
+        if (col < rank) dst[col] = o[n][2 * half] * inv;
+        if (col + 1 < rank) dst[col + 1] = o[n][2 * half + 1] * inv;
+      }
+    } else {
+      float* share = part + (((size_t)t * heads + h) * ranges + blockIdx.z) * (rank + 2);
+      if (warp == 0 && tg == 0) {
+        share[0] = m;
+        share[1] = l;
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int col = warp * CW + n * 8 + 2 * tg;
+        if (col < rank) share[2 + col] = o[n][2 * half];
+        if (col + 1 < rank) share[2 + col + 1] = o[n][2 * half + 1];
+      }
+    }
+  }
+}
+
+}  // namespace cie
+
+// 1 if the kernel takes these sizes (bfloat16 pages; latent and rotated part multiples of 8, latent up to 512).
+extern "C" int cie_latent_attention_tensor_supports(int rank, int rot) {
+  return rank % 8 == 0 && rot % 8 == 0 && rank >= 8 && rot >= 8 && rank <= 512 ? 1 : 0;
+}
+
+extern "C" int cie_latent_attention_tensor(const float* q_abs, const float* q_raw, int q_raw_stride, int q_raw_head,
+                                           float* out, float* part, const void* c_pool, const void* r_pool,
+                                           const int* positions, const int* request_of_token, const int* table,
+                                           int table_width, int num_pages, const float* inv_freq, float magnitude,
+                                           int interleaved, int rot_dims, const float* sink, int tokens, int heads,
+                                           int rank, int rot, int page_size, float scale, int range_keys, int ranges,
+                                           int* err, void* stream) {
+  using namespace cie;
+  if (tokens <= 0) return 0;
+  if (!cie_latent_attention_tensor_supports(rank, rot)) CIE_FAIL("latent_attention_tensor: sizes %d + %d", rank, rot);
+  if (range_keys < kTile || range_keys % kTile) CIE_FAIL("latent_attention_tensor: key ranges are multiples of %d", kTile);
+  if (ranges < 1 || ranges > 65535 || (ranges > 1 && !part)) CIE_FAIL("latent_attention_tensor: %d key ranges", ranges);
+  const int nt = (rank + 63) / 64;
+  const Layout lay = Layout::of(rank, rot, 8 * nt);
+  const size_t smem = lay.bytes();
+  if (smem > 220 * 1024) CIE_FAIL("latent_attention_tensor: %zu bytes of shared memory", smem);
+  const dim3 grid(tokens, (heads + kRows - 1) / kRows, ranges);
+#define CIE_LATENT_TENSOR(NT)                                                                                       \
+  {                                                                                                                 \
+    static bool raised = false;                                                                                     \
+    if (!raised) {                                                                                                  \
+      if (cudaFuncSetAttribute(latent_attention_tensor_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                               220 * 1024) != cudaSuccess)                                                          \
+        CIE_FAIL("latent_attention_tensor: cannot raise the shared memory limit");                                  \
+      raised = true;                                                                                                \
+    }                                                                                                               \
+    CIE_LAUNCH("latent_attention_tensor", latent_attention_tensor_kernel<NT>, grid, dim3(kWarps * 32), smem,        \
+               (cudaStream_t)stream, q_abs, q_raw, q_raw_stride, q_raw_head, out, part, (const bf16*)c_pool,        \
+               (const bf16*)r_pool, positions, request_of_token, table, table_width, num_pages, inv_freq, magnitude, \
+               interleaved, rot_dims, sink, heads, rank, rot, page_size, scale, range_keys, ranges, err);           \
+  }
+  switch (nt) {
+    case 1: CIE_LATENT_TENSOR(1) break;
+    case 2: CIE_LATENT_TENSOR(2) break;
+    case 3: CIE_LATENT_TENSOR(3) break;
+    case 4: CIE_LATENT_TENSOR(4) break;
+    case 5: CIE_LATENT_TENSOR(5) break;
+    case 6: CIE_LATENT_TENSOR(6) break;
+    case 7: CIE_LATENT_TENSOR(7) break;
+    default: CIE_LATENT_TENSOR(8) break;
+  }
+#undef CIE_LATENT_TENSOR
+  return 0;
+}

@@ -448,8 +448,16 @@ class Ops:
             self._latent_attention = lib.function(
                 "cie_latent_attention",
                 [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, v, v])
+            self._latent_merge = lib.function("cie_latent_merge", [v, v, v, v, i, i, i, i, i, v])
             self.latent_max_rank = int(lib.handle.cie_latent_attention_max_rank())
             self._latent_lib = lib
+            self._latent_tensor = None
+            if self.code == BF16 and os.environ.get("CIE_LATENT_TENSOR", "1") != "0":
+                tensor = _Lib(load_library("latent_tensor.cu"))
+                self._latent_tensor = tensor.function(
+                    "cie_latent_attention_tensor",
+                    [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, v, v])
+                self._latent_tensor_supports = tensor.handle.cie_latent_attention_tensor_supports
 
     def latent_prepare(self, down: Any, q_out: Any, q_gain: Any, kv_gain: Any, ctx: Any, kv: Any, rotation: Any,
                        q_rank: int, rank: int, rot: int, eps: float, has_kv: bool, write_cache: bool) -> None:
@@ -488,12 +496,15 @@ class Ops:
         part of ``q_raw`` (float32; head h starts at column ``h * q_raw_head``; rotated here) meets the key
         parts; ``out`` float32 [T, heads, rank] is the weighted sum of the latents.  ``sink`` (float32
         [heads] or None) adds exp(sink_h) to the softmax denominator.  With few tokens the keys are cut
-        into ranges over CTAs and joined by a second kernel."""
+        into ranges over CTAs and joined by a second kernel.  bfloat16 pages whose two parts are multiples
+        of 8 elements run on the tensor cores (16 heads of a token a tile), everything else on the plain
+        kernel (8 heads a CTA, a warp each)."""
         self._flush()
         self._load_latent()
         tokens = q_latent.shape[0]
         table = ctx.block_tables[kv.group]
-        groups = -(-heads // 8)
+        tensor = self._latent_tensor is not None and bool(self._latent_tensor_supports(rank, rot))
+        groups = -(-heads // (16 if tensor else 8))
         ranges, range_keys, scratch = 1, 1 << 30, None
         if tokens * groups < self.sm_count:
             range_keys = 128
@@ -503,6 +514,16 @@ class Ops:
         else:
             ranges, range_keys = 1, 1 << 30
         self.launches += 2 if ranges > 1 else 1
+        if tensor:
+            self._latent_tensor(_ptr(q_latent), _ptr(q_raw), q_raw.stride(0), q_raw_head, _ptr(out), _ptr(scratch),
+                                _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token), _ptr(table),
+                                table.shape[1], kv.num_pages, _ptr(rotation.inv_freq), float(rotation.magnitude),
+                                int(rotation.interleaved), int(rotation.dims), _ptr(sink), tokens, heads, rank, rot,
+                                kv.page_size, float(scale), range_keys, ranges, _ptr(self.error_word), self.stream)
+            if ranges > 1:
+                self._latent_merge(_ptr(scratch), _ptr(out), _ptr(ctx.positions), _ptr(sink), tokens, heads, rank,
+                                   range_keys, ranges, self.stream)
+            return
         self._latent_attention(_ptr(q_latent), _ptr(q_raw), q_raw.stride(0), q_raw_head, _ptr(out), _ptr(scratch),
                                _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token), _ptr(table),
                                table.shape[1], kv.num_pages, _ptr(rotation.inv_freq), float(rotation.magnitude),
