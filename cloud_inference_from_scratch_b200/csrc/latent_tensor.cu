@@ -146,8 +146,6 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
       qs[r * ld + rank + i] = __float2bfloat16_rn(q_raw[(size_t)t * q_raw_stride + (size_t)(h0 + r) * q_raw_head + i]);
   }
 
-  const int chunks = D / 8;                 // 16-byte pieces of a row [c | kr] (rank and rot are multiples of 8)
-  const int rank_chunks = rank / 8;
   auto fetch = [&](int base, int buf) {
     // which row of the pools every key of the tile lives in
     if (tid < kTile) {
@@ -162,14 +160,20 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
     }
   };
   auto copy = [&](int buf) {
+    // warp w brings keys 8w .. 8w + 7 of the tile, a lane every 32nd 16-byte piece of a row
     bf16* dst = ks + (size_t)buf * kTile * ld;
-    for (int e = tid; e < kTile * chunks; e += blockDim.x) {
-      const int j = e / chunks, c = e % chunks;
+#pragma unroll
+    for (int jj = 0; jj < kTile / kWarps; ++jj) {
+      const int j = warp * (kTile / kWarps) + jj;
       const long long r = row_of[buf * kTile + j];
       const bool valid = r >= 0;
-      const bf16* src = c < rank_chunks ? c_pool + (valid ? (size_t)r * rank + c * 8 : 0)
-                                        : r_pool + (valid ? (size_t)r * rot + (c - rank_chunks) * 8 : 0);
-      cp_async16(dst + j * ld + c * 8, src, valid);
+      const bf16* c_src = c_pool + (valid ? (size_t)r * rank : 0);
+      const bf16* r_src = r_pool + (valid ? (size_t)r * rot : 0);
+      bf16* row = dst + j * ld;
+      for (int c = lane * 8; c < D; c += 256) {
+        const bf16* src = c < rank ? c_src + (valid ? c : 0) : r_src + (valid ? c - rank : 0);
+        cp_async16(row + c, src, valid);
+      }
     }
     cp_async_commit();
   };
@@ -196,14 +200,28 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
     // scores of keys 8 * warp .. + 7 for the 16 rows
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     {
+      // two chains of dependent products (even and odd steps of 16), joined at the end
+      float s2[4] = {0.f, 0.f, 0.f, 0.f};
       const bf16* a_ptr = qs + (lane & 15) * ld + (lane >> 4) * 8;
       const bf16* b_ptr = kt + (warp * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8;
-      for (int k0 = 0; k0 < lay.depth; k0 += 16) {
+      int k0 = 0;
+      for (; k0 + 32 <= lay.depth; k0 += 32) {
+        uint32_t a[4], a2[4], b0, b1, b2, b3;
+        ldsm_x4(a, a_ptr + k0);
+        ldsm_x2(b0, b1, b_ptr + k0);
+        ldsm_x4(a2, a_ptr + k0 + 16);
+        ldsm_x2(b2, b3, b_ptr + k0 + 16);
+        mma_bf16(s, a, b0, b1);
+        mma_bf16(s2, a2, b2, b3);
+      }
+      if (k0 < lay.depth) {
         uint32_t a[4], b0, b1;
         ldsm_x4(a, a_ptr + k0);
         ldsm_x2(b0, b1, b_ptr + k0);
         mma_bf16(s, a, b0, b1);
       }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i] += s2[i];
     }
     const int key0 = base + warp * 8 + 2 * tg;
     const bool in0 = key0 < end, in1 = key0 + 1 < end;

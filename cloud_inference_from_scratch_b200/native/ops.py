@@ -540,6 +540,9 @@ class Ops:
             self._delta_scan = lib.function(
                 "cie_delta_scan", [v, i, i, i, i, i, v, i, v, v, v, i, v, v, v, v, i, i, i, i, v, v])
             self._group_gate_norm = lib.function("cie_group_gate_norm", [v, i, v, i, v, v, i, i, i, i, f, i, v])
+            self._delta_stream = lib.function(
+                "cie_delta_stream", [v, i, i, i, i, i, v, i, v, v, v, v, i, v, v, v, v, i, i, i, i, i, v, v])
+            lib.handle.cie_delta_stream_floats.restype = ctypes.c_longlong
             self.delta_max_dim = int(lib.handle.cie_delta_max_dim())
             self._delta_lib = lib
 
@@ -555,11 +558,23 @@ class Ops:
         """Runs the generalized delta rule over every request's new tokens from the state in its slot
         (``state``: float32 [slots, heads, dim, dim]).  ``proj`` float32 rows hold r, k, v and the
         removal projection from the columns ``offsets``; ``decay`` float32 [T, heads * dim] is the decay
-        projection; both biases are added here; ``out`` float32 [T, heads * dim]."""
+        projection; both biases are added here; ``out`` float32 [T, heads * dim].  A step of single tokens
+        runs one kernel that works the rates out as it goes; a step with prompt portions (eight tokens a
+        request or more on average) first works out, for all tokens at once, what the recurrence reads
+        and then streams it through a ring of copies: the same additions in the same order."""
         self._flush()
         self._load_delta()
-        self.launches += 1
         r_off, k_off, v_off, a_off = offsets
+        tokens = proj.shape[0]
+        if tokens >= 8 * ctx.num_requests and os.environ.get("CIE_DELTA_STREAM", "1") != "0":
+            packed = self.scratch("delta.packed", int(self._delta_lib.handle.cie_delta_stream_floats(tokens, heads, dim)))
+            self.launches += 2
+            self._delta_stream(_ptr(proj), proj.stride(0), r_off, k_off, v_off, a_off, _ptr(decay), decay.stride(0),
+                               _ptr(decay_bias), _ptr(removal_bias), _ptr(packed), _ptr(out), out.stride(0), _ptr(state),
+                               _ptr(ctx.query_start), _ptr(ctx.slots), _ptr(ctx.request_active), tokens,
+                               ctx.num_requests, heads, dim, state.shape[0], _ptr(self.error_word), self.stream)
+            return
+        self.launches += 1
         self._delta_scan(_ptr(proj), proj.stride(0), r_off, k_off, v_off, a_off, _ptr(decay), decay.stride(0),
                          _ptr(decay_bias), _ptr(removal_bias), _ptr(out), out.stride(0), _ptr(state),
                          _ptr(ctx.query_start), _ptr(ctx.slots), _ptr(ctx.request_active), ctx.num_requests, heads, dim,

@@ -416,11 +416,12 @@ def test_attention_over_latent_rows_with_one_key_that_stands_out(dtype, with_sin
             assert (last[1] - latent_rows[n - 1].double()).abs().max() < 0.05 + (0.2 if with_sink else 0.0)
 
 
+@pytest.mark.parametrize("first_lengths", [[13, 1, 6], [40, 3, 33]])      # the second: the two-kernel form for portions
 @pytest.mark.parametrize("dim", [1, 7, 16, 33, 64, 100, 128])
-def test_delta_scan_carries_its_state_between_steps_and_leaves_padding_rows_alone(dim):
+def test_delta_scan_carries_its_state_between_steps_and_leaves_padding_rows_alone(dim, first_lengths):
     rt = runtime("float32")
     heads = 3
-    lengths = [13, 1, 6]
+    lengths = list(first_lengths)
     width = heads * dim
     slots = torch.tensor([2, 0, 3], dtype=torch.int32)
     state = torch.zeros(5, heads, dim, dim).cuda()
@@ -452,6 +453,27 @@ def test_delta_scan_carries_its_state_between_steps_and_leaves_padding_rows_alon
             close(state[slots[r]], held, "float32", scale=max(1.0, float(after.abs().max())))
         lengths = [1, 1, 4]
     assert float(state[1].abs().max()) == 0 and float(state[4].abs().max()) == 0      # other slots untouched
+
+
+@pytest.mark.parametrize("dim", [12, 64, 128])
+def test_delta_rule_in_one_kernel_and_in_two_adds_in_the_same_order(monkeypatch, dim):
+    rt = runtime("float32")
+    heads, lengths = 2, [50, 9, 31]
+    width, tokens = heads * dim, sum(lengths)
+    proj, decay = rand(tokens, 5 * width, seed=1), rand(tokens, width, seed=2)
+    w0, a0 = rand(width, seed=3), rand(width, seed=4)
+    starts = torch.tensor([0, *np.cumsum(lengths)], dtype=torch.int32)
+    ctx = SimpleNamespace(query_start=starts.cuda(), slots=torch.tensor([1, 0, 2], dtype=torch.int32).cuda(), num_requests=3,
+                          request_active=torch.ones(3, dtype=torch.int32).cuda())
+    seen = []
+    for switch in ("1", "0"):
+        monkeypatch.setenv("CIE_DELTA_STREAM", switch)
+        state = rand(3, heads, dim, dim, seed=5, scale=0.3).cuda()
+        out = torch.empty(tokens, width, dtype=torch.float32).cuda()
+        rt.ops.delta_scan(proj.cuda(), (0, width, 2 * width, 4 * width), decay.cuda(), w0.cuda(), a0.cuda(), out, state, ctx, heads, dim)
+        rt.ops.check_errors()
+        seen.append((out.cpu(), state.cpu()))
+    assert torch.equal(seen[0][0], seen[1][0]) and torch.equal(seen[0][1], seen[1][1])
 
 
 def test_delta_rule_unlearns_along_its_key():
