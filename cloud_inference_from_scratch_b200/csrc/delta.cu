@@ -7,8 +7,9 @@
 //
 // with a decay w_t = exp(-exp(-1/2) * sigmoid(d_t + w0)) and a removal rate a_t = sigmoid(e_t + a0) per
 // head and key channel.  r, k, v, e and d arrive as float32 projections of the token; everything from
-// there on is float32.  A value column of S never meets another one, so four lanes share a column
-// (each a quarter of its rows, kept in registers) and join their sums by shuffles.
+// there on is float32.  A value column of S never meets another one, so eight lanes share a column
+// (each an eighth of its rows, kept in registers) and join their sums by shuffles: what bounds the
+// recurrence is the chain of dependent steps of one token, and more lanes a column shorten it.
 //
 // A second kernel divides every head of o by its own root mean square, multiplies by a gain vector and
 // by sigmoid(gate), and rounds once.
@@ -21,7 +22,7 @@ CIE_DEFINE_LAST_ERROR()
 
 namespace cie {
 
-constexpr int kDeltaLanes = 4;         // lanes that share a value column
+constexpr int kDeltaLanes = 8;         // lanes that share a value column
 constexpr int kDeltaMaxDim = 128;
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
@@ -121,6 +122,7 @@ delta_scan_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
     for (int i = 0; i < R; ++i) dot = fmaf(u_s[buf][part * R + i], s[i], dot);
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 4);
     float o = 0.f;
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -130,6 +132,7 @@ delta_scan_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
     }
     o += __shfl_xor_sync(0xffffffffu, o, 1);
     o += __shfl_xor_sync(0xffffffffu, o, 2);
+    o += __shfl_xor_sync(0xffffffffu, o, 4);
     if (live && part == 0) out[(size_t)t * out_stride + base + column] = o;
     // the buffers of token t are written again for token t + 2, after the barrier of token t + 1
   }
@@ -252,6 +255,7 @@ delta_stream_kernel(const float* __restrict__ packed, float* __restrict__ out, i
     }
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 4);
     float o = 0.f;
 #pragma unroll
     for (int i = 0; i < R / 4; ++i) {
@@ -267,6 +271,7 @@ delta_stream_kernel(const float* __restrict__ packed, float* __restrict__ out, i
     }
     o += __shfl_xor_sync(0xffffffffu, o, 1);
     o += __shfl_xor_sync(0xffffffffu, o, 2);
+    o += __shfl_xor_sync(0xffffffffu, o, 4);
     if (live && part == 0) out[(size_t)t * out_stride + base + column] = o;
   }
   asm volatile("cp.async.wait_group 0;\n" ::);
@@ -333,16 +338,16 @@ extern "C" int cie_delta_scan(const float* proj, int proj_stride, int r_off, int
   CIE_LAUNCH("delta_scan", delta_scan_kernel<R>, grid, dim3(threads), 0, (cudaStream_t)stream, proj, proj_stride, \
              r_off, k_off, v_off, a_off, decay, decay_stride, decay_bias, removal_bias, out, out_stride, state,  \
              query_start, slots, request_active, heads, dim, max_slots, err)
-  if (dim <= 32) { CIE_DELTA_SCAN(8); }
-  else if (dim <= 64) { CIE_DELTA_SCAN(16); }
-  else { CIE_DELTA_SCAN(32); }
+  if (dim <= 32) { CIE_DELTA_SCAN(4); }
+  else if (dim <= 64) { CIE_DELTA_SCAN(8); }
+  else { CIE_DELTA_SCAN(16); }
 #undef CIE_DELTA_SCAN
   return 0;
 }
 
 // Floats of scratch memory the two-kernel form wants for `tokens` tokens.
 extern "C" long long cie_delta_stream_floats(int tokens, int heads, int dim) {
-  const int pad = cie::kDeltaLanes * (dim <= 32 ? 8 : dim <= 64 ? 16 : 32);
+  const int pad = cie::kDeltaLanes * (dim <= 32 ? 4 : dim <= 64 ? 8 : 16);
   return (long long)tokens * heads * cie::kDeltaFields * pad;
 }
 
@@ -354,16 +359,16 @@ extern "C" int cie_delta_stream(const float* proj, int proj_stride, int r_off, i
   using namespace cie;
   if (requests <= 0 || tokens <= 0) return 0;
   if (dim < 1 || dim > kDeltaMaxDim) CIE_FAIL("delta_stream: head size %d is outside 1..%d", dim, kDeltaMaxDim);
-  const int rows = dim <= 32 ? 8 : dim <= 64 ? 16 : 32;
+  const int rows = dim <= 32 ? 4 : dim <= 64 ? 8 : 16;
   const int pad = kDeltaLanes * rows;
   CIE_LAUNCH("delta_prepare", delta_prepare_kernel, dim3(tokens, heads), dim3(32), 0, (cudaStream_t)stream, proj,
              proj_stride, r_off, k_off, v_off, a_off, decay, decay_stride, decay_bias, removal_bias, packed, heads, dim, pad);
   const int threads = (kDeltaLanes * dim + 31) / 32 * 32;
   const dim3 grid(requests, heads);
 #define CIE_DELTA_STREAM(R)                                                                                         CIE_LAUNCH("delta_stream", delta_stream_kernel<R>, grid, dim3(threads), 0, (cudaStream_t)stream, packed, out,                out_stride, state, query_start, slots, request_active, heads, dim, max_slots, err)
-  if (rows == 8) { CIE_DELTA_STREAM(8); }
-  else if (rows == 16) { CIE_DELTA_STREAM(16); }
-  else { CIE_DELTA_STREAM(32); }
+  if (rows == 4) { CIE_DELTA_STREAM(4); }
+  else if (rows == 8) { CIE_DELTA_STREAM(8); }
+  else { CIE_DELTA_STREAM(16); }
 #undef CIE_DELTA_STREAM
   return 0;
 }

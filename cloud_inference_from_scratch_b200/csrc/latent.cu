@@ -143,6 +143,41 @@ head_linear_kernel(const float* __restrict__ x, int x_stride, int x_head, const 
   }
 }
 
+// For many tokens the products per head run as one batched library product over [heads, T, K] x
+// [heads, K, N]; these two kernels carry the rows there and back.
+// gather: dst[h][t][k] = bfloat16(x[t * x_stride + h * x_head + k])
+__global__ void head_gather_kernel(const float* __restrict__ x, int x_stride, int x_head, __nv_bfloat16* __restrict__ dst,
+                                   int tokens, int heads, int K) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t total = (size_t)tokens * heads * K;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const int k = (int)(e % K);
+    const size_t th = e / K;
+    const int h = (int)(th % heads);
+    const size_t t = th / heads;
+    dst[((size_t)h * tokens + t) * K + k] = __float2bfloat16_rn(x[t * x_stride + (size_t)h * x_head + k]);
+  }
+}
+
+// scatter: out[t * out_stride + h * out_head + j] = y[h][t][j] (* sigmoid(gate[t * gate_stride + h * N + j]))
+template <typename TO>
+__global__ void head_scatter_kernel(const __nv_bfloat16* __restrict__ y, TO* __restrict__ out, int out_stride, int out_head,
+                                    const float* __restrict__ gate, int gate_stride, int tokens, int heads, int N) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t total = (size_t)tokens * heads * N;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const int j = (int)(e % N);
+    const size_t th = e / N;
+    const int h = (int)(th % heads);
+    const size_t t = th / heads;
+    float v = __bfloat162float(y[((size_t)h * tokens + t) * N + j]);
+    if (gate) v *= 1.f / (1.f + expf(-gate[t * gate_stride + (size_t)h * N + j]));
+    out[t * out_stride + (size_t)h * out_head + j] = from_float<TO>(v);
+  }
+}
+
 // ---------------------------------------------------------------- attention
 // One CTA per (token, group of kAttnHeads heads, key range); a warp per head.  The rows
 // [c_j | kr_j] of 32 keys at a time are staged in shared memory as float32 and shared by the warps:
@@ -349,6 +384,30 @@ extern "C" int cie_head_linear(const float* x, int x_stride, int x_head, const v
   else if (w_dtype == kBFloat16 && out_dtype == kBFloat16) { CIE_HEAD_LINEAR(__nv_bfloat16, __nv_bfloat16); }
   else CIE_FAIL("head_linear: weight dtype %d with output dtype %d", w_dtype, out_dtype);
 #undef CIE_HEAD_LINEAR
+  return 0;
+}
+
+extern "C" int cie_head_gather(const float* x, int x_stride, int x_head, void* dst, int tokens, int heads, int K,
+                               void* stream) {
+  using namespace cie;
+  const size_t total = (size_t)tokens * heads * K;
+  if (total == 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  CIE_LAUNCH("head_gather", head_gather_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, x_stride, x_head,
+             (__nv_bfloat16*)dst, tokens, heads, K);
+  return 0;
+}
+
+extern "C" int cie_head_scatter(const void* y, void* out, int out_stride, int out_head, const float* gate,
+                                int gate_stride, int tokens, int heads, int N, int out_dtype, void* stream) {
+  using namespace cie;
+  const size_t total = (size_t)tokens * heads * N;
+  if (total == 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  DISPATCH_DTYPE(out_dtype, "head_scatter", {
+    CIE_LAUNCH("head_scatter", head_scatter_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+               (const __nv_bfloat16*)y, (T*)out, out_stride, out_head, gate, gate_stride, tokens, heads, N);
+  })
   return 0;
 }
 

@@ -46,6 +46,17 @@ __device__ __forceinline__ void ldsm_x2(uint32_t& r0, uint32_t& r1, const void* 
 __device__ __forceinline__ void ldsm_x2_trans(uint32_t& r0, uint32_t& r1, const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(smem_u32(p)));
 }
+// the same loads by shared-memory address (the conversion from a pointer is done once, outside the loops)
+__device__ __forceinline__ void ldsm_x4_at(uint32_t (&r)[4], uint32_t address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldsm_x2_at(uint32_t& r0, uint32_t& r1, uint32_t address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(address));
+}
+__device__ __forceinline__ void ldsm_x2_trans_at(uint32_t& r0, uint32_t& r1, uint32_t address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(address));
+}
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -184,6 +195,13 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
   float m0 = -FLT_MAX, m1 = -FLT_MAX;     // running maxima of rows g and g + 8 (the same in every warp)
   float l0 = 0.f, l1 = 0.f;               // this thread's share of the rows' sums (its own keys only)
 
+  // shared-memory addresses of this lane's fragment rows: query rows, the keys of this warp, the
+  // weights, and the latent columns of this warp (each plus a tile's offset inside the loops)
+  const uint32_t q_at = smem_u32(qs + (lane & 15) * ld + (lane >> 4) * 8);
+  const uint32_t k_at = smem_u32(ks + (warp * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
+  const uint32_t p_at = smem_u32(ps + (lane & 15) * PLD + (lane >> 4) * 8);
+  const uint32_t v_at = smem_u32(ks + (lane & 15) * ld + warp * CW);
+
   const int tiles = (end - begin + kTile - 1) / kTile;
   fetch(begin, 0);
   __syncthreads();
@@ -195,29 +213,28 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
     cp_async_wait<0>();
     __syncthreads();          // [A] tile i has landed; everybody is done with tile i - 1, the weights and the maxima
     if (i + 1 < tiles) copy(buf ^ 1);
-    const bf16* kt = ks + (size_t)buf * kTile * ld;
 
     // scores of keys 8 * warp .. + 7 for the 16 rows
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     {
       // two chains of dependent products (even and odd steps of 16), joined at the end
       float s2[4] = {0.f, 0.f, 0.f, 0.f};
-      const bf16* a_ptr = qs + (lane & 15) * ld + (lane >> 4) * 8;
-      const bf16* b_ptr = kt + (warp * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8;
+      uint32_t a_at = q_at;
+      uint32_t b_at = k_at + (uint32_t)buf * (kTile * ld * 2);
       int k0 = 0;
-      for (; k0 + 32 <= lay.depth; k0 += 32) {
+      for (; k0 + 32 <= lay.depth; k0 += 32, a_at += 64, b_at += 64) {
         uint32_t a[4], a2[4], b0, b1, b2, b3;
-        ldsm_x4(a, a_ptr + k0);
-        ldsm_x2(b0, b1, b_ptr + k0);
-        ldsm_x4(a2, a_ptr + k0 + 16);
-        ldsm_x2(b2, b3, b_ptr + k0 + 16);
+        ldsm_x4_at(a, a_at);
+        ldsm_x2_at(b0, b1, b_at);
+        ldsm_x4_at(a2, a_at + 32);
+        ldsm_x2_at(b2, b3, b_at + 32);
         mma_bf16(s, a, b0, b1);
         mma_bf16(s2, a2, b2, b3);
       }
       if (k0 < lay.depth) {
         uint32_t a[4], b0, b1;
-        ldsm_x4(a, a_ptr + k0);
-        ldsm_x2(b0, b1, b_ptr + k0);
+        ldsm_x4_at(a, a_at);
+        ldsm_x2_at(b0, b1, b_at);
         mma_bf16(s, a, b0, b1);
       }
 #pragma unroll
@@ -268,17 +285,16 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
     }
     __syncthreads();          // [C] all weights of the tile are in shared memory
     {
-      const bf16* a_ptr = ps + (lane & 15) * PLD + (lane >> 4) * 8;
-      const bf16* b_ptr = kt + (lane & 15) * ld + warp * CW;
+      uint32_t b_at = v_at + (uint32_t)buf * (kTile * ld * 2);
 #pragma unroll
-      for (int k0 = 0; k0 < kTile; k0 += 16) {
+      for (int k0 = 0; k0 < kTile; k0 += 16, b_at += 16 * ld * 2) {
         uint32_t hi[4], lo[4];
-        ldsm_x4(hi, a_ptr + k0);
-        ldsm_x4(lo, a_ptr + kRows * PLD + k0);
+        ldsm_x4_at(hi, p_at + k0 * 2);
+        ldsm_x4_at(lo, p_at + (kRows * PLD + k0) * 2);
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
           uint32_t b0, b1;
-          ldsm_x2_trans(b0, b1, b_ptr + k0 * ld + n * 8);
+          ldsm_x2_trans_at(b0, b1, b_at + n * 16);
           mma_bf16(o[n], hi, b0, b1);
           mma_bf16(o[n], lo, b0, b1);
         }

@@ -449,6 +449,8 @@ class Ops:
                 "cie_latent_attention",
                 [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, v, v])
             self._latent_merge = lib.function("cie_latent_merge", [v, v, v, v, i, i, i, i, i, v])
+            self._head_gather = lib.function("cie_head_gather", [v, i, i, v, i, i, i, v])
+            self._head_scatter = lib.function("cie_head_scatter", [v, v, i, i, v, i, i, i, i, i, v])
             self.latent_max_rank = int(lib.handle.cie_latent_attention_max_rank())
             self._latent_lib = lib
             self._latent_tensor = None
@@ -480,10 +482,29 @@ class Ops:
         """A product per head: ``out[t, h, :N] = x[t, h, :K] @ weight[h]`` with ``weight`` [heads, K, N] in
         the compute dtype, ``x`` float32 (head h of a row starts at column ``h * x_head``), ``out`` float32
         or the compute dtype (head h at column ``h * out_head``); sums in float32, k ascending.  With
-        ``gate`` (float32 [T, heads * N], may be a view of columns) the result is multiplied by sigmoid(gate)."""
+        ``gate`` (float32 [T, heads * N], may be a view of columns) the result is multiplied by sigmoid(gate).
+
+        More than 16 tokens in bfloat16 run as ONE batched library product (the framework's rule for
+        matrix products of that many rows): the rows are gathered head-major and rounded to bfloat16, the
+        product's bfloat16 result is carried back (with the gate) by a second small kernel."""
         self._flush()
         self._load_latent()
         _, depth, width = weight.shape
+        tokens = x.shape[0]
+        if (self.code == BF16 and tokens > STREAM_MAX_ROWS and weight.dtype == self.torch.bfloat16
+                and os.environ.get("CIE_HEAD_BATCHED", "1") != "0"):
+            torch = self.torch
+            rows = self.scratch("head.rows", (heads * tokens * depth + 1) // 2).view(torch.bfloat16)
+            rows = rows[: heads * tokens * depth].view(heads, tokens, depth)
+            result = self.scratch("head.result", (heads * tokens * width + 1) // 2).view(torch.bfloat16)
+            result = result[: heads * tokens * width].view(heads, tokens, width)
+            self.launches += 3
+            self._head_gather(_ptr(x), x.stride(0), x_head, _ptr(rows), tokens, heads, depth, self.stream)
+            torch.bmm(rows, weight, out=result)
+            self._head_scatter(_ptr(result), _ptr(out), out.stride(0), out_head, _ptr(gate),
+                               gate.stride(0) if gate is not None else 0, tokens, heads, width, self._code_of(out),
+                               self.stream)
+            return
         self.launches += 1
         self._head_linear(_ptr(x), x.stride(0), x_head, _ptr(weight), _ptr(out), out.stride(0), out_head, _ptr(gate),
                           gate.stride(0) if gate is not None else 0, x.shape[0], heads, depth, width,

