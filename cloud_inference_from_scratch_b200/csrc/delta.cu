@@ -150,15 +150,18 @@ delta_scan_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
 // exponentials of the rates.  Two kernels instead: `delta_prepare` computes, for all tokens at once,
 // what the recurrence reads (w, a * u, u, k, r, v per head, float32, each padded with zeros to the rows
 // the lanes keep) and `delta_stream` walks a request's tokens reading those rows through a ring of
-// cp.async stages, several tokens ahead.  The arithmetic and its order are those of the scan.
-constexpr int kDeltaStages = 8;
+// cp.async stages, several tokens ahead.  The arithmetic is that of the scan; the sums over a column's
+// rows are added in another order (four chains a thread instead of a chain a lane).
+constexpr int kDeltaStages = 3;      // stages of the ring
+constexpr int kDeltaChunk = 4;       // tokens of a stage: the block meets once a stage, not once a token
 constexpr int kDeltaFields = 6;      // w, a * u, u, k, r, v
 
 // grid (tokens, heads), one warp or more; `pad` = rows as the stream kernel's lanes see them.
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, int r_off, int k_off, int v_off, int a_off,
                      const float* __restrict__ decay, int decay_stride, const float* __restrict__ decay_bias,
-                     const float* __restrict__ removal_bias, float* __restrict__ packed, int heads, int dim, int pad) {
+                     const float* __restrict__ removal_bias, float* __restrict__ packed, int tokens, int heads, int dim,
+                     int pad) {
   __shared__ float scratch[33];
   pdl_wait();
   pdl_trigger();
@@ -172,7 +175,7 @@ delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, int r_off,
   // the scan adds a warp's 32 partial sums; here a block of one warp does the same
   const float total = block_sum(sq, scratch);
   const float inv = rsqrtf(total + 1e-6f);
-  float* dst = packed + ((size_t)t * heads + head) * kDeltaFields * pad;
+  float* dst = packed + ((size_t)head * tokens + t) * kDeltaFields * pad;     // head-major: a head's tokens follow each other
   for (int i = threadIdx.x; i < pad; i += blockDim.x) {
     float w = 0.f, au = 0.f, u = 0.f, k = 0.f, r = 0.f, v = 0.f;
     if (i < dim) {
@@ -196,19 +199,21 @@ __device__ __forceinline__ void delta_cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
 }
 
-template <int R>
-__global__ void __launch_bounds__(kDeltaLanes * kDeltaMaxDim)
+// One thread a value column with ALL its rows in registers: every read of a token's row is then the
+// same address for the whole warp (one shared-memory wavefront a load, where lanes that share a column
+// read eight different places), and no sum crosses lanes.  P = rows as padded (32, 64 or 128).
+template <int P>
+__global__ void __launch_bounds__(kDeltaMaxDim)
 delta_stream_kernel(const float* __restrict__ packed, float* __restrict__ out, int out_stride, float* __restrict__ state,
                     const int* __restrict__ query_start, const int* __restrict__ slots,
-                    const int* __restrict__ request_active, int heads, int dim, int max_slots, int* err) {
-  constexpr int kPad = kDeltaLanes * R;
-  constexpr int kRow = kDeltaFields * kPad;          // floats of one token and head
-  __shared__ __align__(16) float ring[kDeltaStages][kRow];
+                    const int* __restrict__ request_active, int tokens, int heads, int dim, int max_slots, int* err) {
+  constexpr int kRow = kDeltaFields * P;             // floats of one token and head
+  __shared__ __align__(16) float ring[kDeltaStages][kDeltaChunk * kRow];
   pdl_wait();
   pdl_trigger();
   const int request = blockIdx.x, head = blockIdx.y;
   const int tid = threadIdx.x;
-  const int column = tid / kDeltaLanes, part = tid % kDeltaLanes;
+  const int column = tid;
   const bool live = column < dim;
   const int slot = slots[request];
   if (slot < 0 || slot >= max_slots) {
@@ -217,70 +222,66 @@ delta_stream_kernel(const float* __restrict__ packed, float* __restrict__ out, i
   }
   const int begin = query_start[request], end = query_start[request + 1];
   float* s_base = state + ((size_t)slot * heads + head) * dim * dim;
-  float s[R];
+  float s[P];
 #pragma unroll
-  for (int i = 0; i < R; ++i) {
-    const int row = part * R + i;
-    s[i] = (live && row < dim) ? s_base[(size_t)row * dim + column] : 0.f;
-  }
-  auto issue = [&](int t) {
-    if (t < end) {
-      const float* src = packed + ((size_t)t * heads + head) * kRow;
-      float* dst = ring[(t - begin) % kDeltaStages];
-      for (int c = tid; c < kRow / 4; c += blockDim.x) delta_cp_async16(dst + 4 * c, src + 4 * c);
+  for (int i = 0; i < P; ++i) s[i] = (live && i < dim) ? s_base[(size_t)i * dim + column] : 0.f;
+  const float* rows = packed + (size_t)head * tokens * kRow;
+  auto issue = [&](int chunk) {
+    const int first = begin + chunk * kDeltaChunk;
+    if (first < end) {
+      const int count = min(kDeltaChunk, end - first) * (kRow / 4);
+      const float* src = rows + (size_t)first * kRow;
+      float* dst = ring[chunk % kDeltaStages];
+      for (int c = tid; c < count; c += blockDim.x) delta_cp_async16(dst + 4 * c, src + 4 * c);
     }
     asm volatile("cp.async.commit_group;\n" ::);
   };
-  for (int i = 0; i < kDeltaStages - 1; ++i) issue(begin + i);
+  for (int i = 0; i < kDeltaStages - 1; ++i) issue(i);
   const int base = head * dim;
   for (int t = begin; t < end; ++t) {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(kDeltaStages - 2));
-    __syncthreads();          // token t has landed; everybody is done with token t - 1, whose stage is filled next
-    issue(t + kDeltaStages - 1);
-    const float* stage = ring[(t - begin) % kDeltaStages];
-    const float4* w4 = reinterpret_cast<const float4*>(stage + part * R);
-    const float4* au4 = reinterpret_cast<const float4*>(stage + kPad + part * R);
-    const float4* u4 = reinterpret_cast<const float4*>(stage + 2 * kPad + part * R);
-    const float4* k4 = reinterpret_cast<const float4*>(stage + 3 * kPad + part * R);
-    const float4* r4 = reinterpret_cast<const float4*>(stage + 4 * kPad + part * R);
-    const float v = stage[5 * kPad + (live ? column : 0)];
-    float dot = 0.f;      // one chain, rows ascending: the order of the scan
-#pragma unroll
-    for (int i = 0; i < R / 4; ++i) {
-      const float4 u = u4[i];
-      dot = fmaf(u.x, s[4 * i], dot);
-      dot = fmaf(u.y, s[4 * i + 1], dot);
-      dot = fmaf(u.z, s[4 * i + 2], dot);
-      dot = fmaf(u.w, s[4 * i + 3], dot);
+    const int chunk = (t - begin) / kDeltaChunk, place = (t - begin) % kDeltaChunk;
+    if (place == 0) {
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(kDeltaStages - 2));
+      __syncthreads();          // the chunk has landed; everybody is done with the chunk before, whose stage is filled next
+      issue(chunk + kDeltaStages - 1);
     }
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-    float o = 0.f;
+    const float* stage = ring[chunk % kDeltaStages] + place * kRow;
+    const float4* w4 = reinterpret_cast<const float4*>(stage);
+    const float4* au4 = reinterpret_cast<const float4*>(stage + P);
+    const float4* u4 = reinterpret_cast<const float4*>(stage + 2 * P);
+    const float4* k4 = reinterpret_cast<const float4*>(stage + 3 * P);
+    const float4* r4 = reinterpret_cast<const float4*>(stage + 4 * P);
+    const float v = stage[5 * P + (live ? column : 0)];
+    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;      // four chains, joined as (d0 + d1) + (d2 + d3)
 #pragma unroll
-    for (int i = 0; i < R / 4; ++i) {
+    for (int i = 0; i < P / 4; ++i) {
+      const float4 u = u4[i];
+      d0 = fmaf(u.x, s[4 * i], d0);
+      d1 = fmaf(u.y, s[4 * i + 1], d1);
+      d2 = fmaf(u.z, s[4 * i + 2], d2);
+      d3 = fmaf(u.w, s[4 * i + 3], d3);
+    }
+    const float dot = (d0 + d1) + (d2 + d3);
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < P / 4; ++i) {
       const float4 w = w4[i], au = au4[i], k = k4[i], r = r4[i];
       s[4 * i] = fmaf(w.x, s[4 * i], fmaf(k.x, v, -au.x * dot));
       s[4 * i + 1] = fmaf(w.y, s[4 * i + 1], fmaf(k.y, v, -au.y * dot));
       s[4 * i + 2] = fmaf(w.z, s[4 * i + 2], fmaf(k.z, v, -au.z * dot));
       s[4 * i + 3] = fmaf(w.w, s[4 * i + 3], fmaf(k.w, v, -au.w * dot));
-      o = fmaf(r.x, s[4 * i], o);
-      o = fmaf(r.y, s[4 * i + 1], o);
-      o = fmaf(r.z, s[4 * i + 2], o);
-      o = fmaf(r.w, s[4 * i + 3], o);
+      o0 = fmaf(r.x, s[4 * i], o0);
+      o1 = fmaf(r.y, s[4 * i + 1], o1);
+      o2 = fmaf(r.z, s[4 * i + 2], o2);
+      o3 = fmaf(r.w, s[4 * i + 3], o3);
     }
-    o += __shfl_xor_sync(0xffffffffu, o, 1);
-    o += __shfl_xor_sync(0xffffffffu, o, 2);
-    o += __shfl_xor_sync(0xffffffffu, o, 4);
-    if (live && part == 0) out[(size_t)t * out_stride + base + column] = o;
+    if (live) out[(size_t)t * out_stride + base + column] = (o0 + o1) + (o2 + o3);
   }
   asm volatile("cp.async.wait_group 0;\n" ::);
   if (request_active[request] && live) {
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-      const int row = part * R + i;
-      if (row < dim) s_base[(size_t)row * dim + column] = s[i];
-    }
+    for (int i = 0; i < P; ++i)
+      if (i < dim) s_base[(size_t)i * dim + column] = s[i];
   }
 }
 
@@ -347,7 +348,7 @@ extern "C" int cie_delta_scan(const float* proj, int proj_stride, int r_off, int
 
 // Floats of scratch memory the two-kernel form wants for `tokens` tokens.
 extern "C" long long cie_delta_stream_floats(int tokens, int heads, int dim) {
-  const int pad = cie::kDeltaLanes * (dim <= 32 ? 4 : dim <= 64 ? 8 : 16);
+  const int pad = dim <= 32 ? 32 : dim <= 64 ? 64 : 128;
   return (long long)tokens * heads * cie::kDeltaFields * pad;
 }
 
@@ -359,16 +360,18 @@ extern "C" int cie_delta_stream(const float* proj, int proj_stride, int r_off, i
   using namespace cie;
   if (requests <= 0 || tokens <= 0) return 0;
   if (dim < 1 || dim > kDeltaMaxDim) CIE_FAIL("delta_stream: head size %d is outside 1..%d", dim, kDeltaMaxDim);
-  const int rows = dim <= 32 ? 4 : dim <= 64 ? 8 : 16;
-  const int pad = kDeltaLanes * rows;
+  const int pad = dim <= 32 ? 32 : dim <= 64 ? 64 : 128;
   CIE_LAUNCH("delta_prepare", delta_prepare_kernel, dim3(tokens, heads), dim3(32), 0, (cudaStream_t)stream, proj,
-             proj_stride, r_off, k_off, v_off, a_off, decay, decay_stride, decay_bias, removal_bias, packed, heads, dim, pad);
-  const int threads = (kDeltaLanes * dim + 31) / 32 * 32;
+             proj_stride, r_off, k_off, v_off, a_off, decay, decay_stride, decay_bias, removal_bias, packed, tokens, heads,
+             dim, pad);
+  const int threads = (dim + 31) / 32 * 32;
   const dim3 grid(requests, heads);
-#define CIE_DELTA_STREAM(R)                                                                                         CIE_LAUNCH("delta_stream", delta_stream_kernel<R>, grid, dim3(threads), 0, (cudaStream_t)stream, packed, out,                out_stride, state, query_start, slots, request_active, heads, dim, max_slots, err)
-  if (rows == 4) { CIE_DELTA_STREAM(4); }
-  else if (rows == 8) { CIE_DELTA_STREAM(8); }
-  else { CIE_DELTA_STREAM(16); }
+#define CIE_DELTA_STREAM(P)                                                                                       \
+  CIE_LAUNCH("delta_stream", delta_stream_kernel<P>, grid, dim3(threads), 0, (cudaStream_t)stream, packed, out,   \
+             out_stride, state, query_start, slots, request_active, tokens, heads, dim, max_slots, err)
+  if (pad == 32) { CIE_DELTA_STREAM(32); }
+  else if (pad == 64) { CIE_DELTA_STREAM(64); }
+  else { CIE_DELTA_STREAM(128); }
 #undef CIE_DELTA_STREAM
   return 0;
 }
