@@ -143,6 +143,68 @@ head_linear_kernel(const float* __restrict__ x, int x_stride, int x_head, const 
   }
 }
 
+// The same product for at most kHeadTokens tokens (a decode step): what bounds it is the walk over K, so K
+// is cut into kFewSlices slices over the warps of a block, a block takes 32 columns of one head, and the
+// slices meet in shared memory and are added in ascending order.
+constexpr int kFewSlices = 8;
+constexpr int kFewColumns = 32;
+constexpr int kFewMaxK = 256;      // rows of x staged at a time
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(kFewSlices * kFewColumns)
+head_linear_few_kernel(const float* __restrict__ x, int x_stride, int x_head, const TW* __restrict__ w,
+                       TO* __restrict__ out, int out_stride, int out_head, const float* __restrict__ gate,
+                       int gate_stride, int tokens, int K, int N) {
+  __shared__ __align__(16) float xs[kFewMaxK][kHeadTokens];                 // 16 KB
+  __shared__ float sums[kFewSlices][kHeadTokens][kFewColumns + 1];
+  pdl_wait();
+  pdl_trigger();
+  const int h = blockIdx.x;
+  const int slice = threadIdx.x / kFewColumns, lane = threadIdx.x % kFewColumns;
+  const int j = blockIdx.y * kFewColumns + lane;
+  const TW* wh = w + (size_t)h * K * N;
+  float acc[kHeadTokens];
+#pragma unroll
+  for (int i = 0; i < kHeadTokens; ++i) acc[i] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += kFewMaxK) {
+    const int kn = min(kFewMaxK, K - k0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < kn * kHeadTokens; e += blockDim.x) {
+      const int i = e / kn, k = e % kn;
+      xs[k][i] = i < tokens ? x[(size_t)i * x_stride + (size_t)h * x_head + k0 + k] : 0.f;
+    }
+    __syncthreads();
+    if (j < N) {
+#pragma unroll 4
+      for (int k = slice; k < kn; k += kFewSlices) {
+        const float wv = to_float(wh[(size_t)(k0 + k) * N + j]);
+        const float4* xv = reinterpret_cast<const float4*>(xs[k]);
+#pragma unroll
+        for (int i = 0; i < kHeadTokens / 4; ++i) {
+          const float4 v = xv[i];
+          acc[4 * i] = fmaf(v.x, wv, acc[4 * i]);
+          acc[4 * i + 1] = fmaf(v.y, wv, acc[4 * i + 1]);
+          acc[4 * i + 2] = fmaf(v.z, wv, acc[4 * i + 2]);
+          acc[4 * i + 3] = fmaf(v.w, wv, acc[4 * i + 3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kHeadTokens; ++i) sums[slice][i][lane] = acc[i];
+  __syncthreads();
+  for (int e = threadIdx.x; e < tokens * kFewColumns; e += blockDim.x) {
+    const int i = e / kFewColumns, c = e % kFewColumns;
+    const int column = blockIdx.y * kFewColumns + c;
+    if (column >= N) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int sl = 0; sl < kFewSlices; ++sl) v += sums[sl][i][c];
+    if (gate) v *= 1.f / (1.f + expf(-gate[(size_t)i * gate_stride + (size_t)h * N + column]));
+    out[(size_t)i * out_stride + (size_t)h * out_head + column] = from_float<TO>(v);
+  }
+}
+
 // For many tokens the products per head run as one batched library product over [heads, T, K] x
 // [heads, K, N]; these two kernels carry the rows there and back.
 // gather: dst[h][t][k] = bfloat16(x[t * x_stride + h * x_head + k])
@@ -327,6 +389,8 @@ latent_attention_kernel(const float* __restrict__ q_abs, const float* __restrict
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ part, float* __restrict__ out, const int* __restrict__ positions,
                     const float* __restrict__ sink, int heads, int rank, int range_keys, int ranges) {
+  constexpr int kHeld = 256;          // weights of this many ranges are worked out once and kept
+  __shared__ float held[kHeld];
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x, h = blockIdx.y;
@@ -334,12 +398,15 @@ latent_merge_kernel(const float* __restrict__ part, float* __restrict__ out, con
   const float* share = part + ((size_t)t * heads + h) * ranges * (rank + 2);
   float top = sink ? sink[h] : -FLT_MAX;
   for (int r = 0; r < used; ++r) top = fmaxf(top, share[(size_t)r * (rank + 2)]);
+  for (int r = threadIdx.x; r < min(used, kHeld); r += blockDim.x) held[r] = expf(share[(size_t)r * (rank + 2)] - top);
+  __syncthreads();
+  auto weight = [&](int r) { return r < kHeld ? held[r] : expf(share[(size_t)r * (rank + 2)] - top); };
   float total = sink ? expf(sink[h] - top) : 0.f;
-  for (int r = 0; r < used; ++r) total += share[(size_t)r * (rank + 2) + 1] * expf(share[(size_t)r * (rank + 2)] - top);
+  for (int r = 0; r < used; ++r) total += share[(size_t)r * (rank + 2) + 1] * weight(r);
   const float inv = 1.f / total;
   for (int col = threadIdx.x; col < rank; col += blockDim.x) {
     float a = 0.f;
-    for (int r = 0; r < used; ++r) a = fmaf(share[(size_t)r * (rank + 2) + 2 + col], expf(share[(size_t)r * (rank + 2)] - top), a);
+    for (int r = 0; r < used; ++r) a = fmaf(share[(size_t)r * (rank + 2) + 2 + col], weight(r), a);
     out[((size_t)t * heads + h) * rank + col] = a * inv;
   }
 }
@@ -374,11 +441,18 @@ extern "C" int cie_head_linear(const float* x, int x_stride, int x_head, const v
                                int heads, int K, int N, int w_dtype, int out_dtype, void* stream) {
   using namespace cie;
   if (tokens <= 0 || heads <= 0 || N <= 0) return 0;
-  const dim3 grid((tokens + kHeadTokens - 1) / kHeadTokens, heads, (N + kHeadColumns - 1) / kHeadColumns);
+  const bool few = tokens <= kHeadTokens;
+  const dim3 grid = few ? dim3(heads, (N + kFewColumns - 1) / kFewColumns)
+                        : dim3((tokens + kHeadTokens - 1) / kHeadTokens, heads, (N + kHeadColumns - 1) / kHeadColumns);
   if (grid.y > 65535 || grid.z > 65535) CIE_FAIL("head_linear: too many heads or columns");
 #define CIE_HEAD_LINEAR(TW, TO)                                                                                   \
-  CIE_LAUNCH("head_linear", (head_linear_kernel<TW, TO>), grid, dim3(kHeadColumns), 0, (cudaStream_t)stream, x,   \
-             x_stride, x_head, (const TW*)w, (TO*)out, out_stride, out_head, gate, gate_stride, tokens, K, N)
+  if (few) {                                                                                                      \
+    CIE_LAUNCH("head_linear", (head_linear_few_kernel<TW, TO>), grid, dim3(kFewSlices * kFewColumns), 0,          \
+               (cudaStream_t)stream, x, x_stride, x_head, (const TW*)w, (TO*)out, out_stride, out_head, gate,     \
+               gate_stride, tokens, K, N);                                                                        \
+  } else                                                                                                          \
+    CIE_LAUNCH("head_linear", (head_linear_kernel<TW, TO>), grid, dim3(kHeadColumns), 0, (cudaStream_t)stream, x, \
+               x_stride, x_head, (const TW*)w, (TO*)out, out_stride, out_head, gate, gate_stride, tokens, K, N)
   if (w_dtype == kFloat32 && out_dtype == kFloat32) { CIE_HEAD_LINEAR(float, float); }
   else if (w_dtype == kBFloat16 && out_dtype == kFloat32) { CIE_HEAD_LINEAR(__nv_bfloat16, float); }
   else if (w_dtype == kBFloat16 && out_dtype == kBFloat16) { CIE_HEAD_LINEAR(__nv_bfloat16, __nv_bfloat16); }

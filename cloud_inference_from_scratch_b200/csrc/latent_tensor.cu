@@ -125,11 +125,13 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
   const int* pages = table + (size_t)request_of_token[t] * table_width;
   const int D = rank + rot;
 
-  // everything starts as zero: padding columns and rows that no copy writes must not hold NaN patterns
+  // what no copy writes starts as zero (padding must not hold NaN patterns): the query rows, the weights,
+  // and the columns of every key row beyond [rank + rot]; rows past the last key are zero-filled by the copies
   {
-    uint4* words = reinterpret_cast<uint4*>(shared_raw);
-    const int count = (int)(((size_t)(kRows + 2 * kTile) * ld + 2 * kRows * PLD) * sizeof(bf16) / 16);
-    for (int i = tid; i < count; i += blockDim.x) words[i] = make_uint4(0, 0, 0, 0);
+    const int pad = ld - D;
+    for (int e = tid; e < kRows * ld; e += blockDim.x) qs[e] = __float2bfloat16_rn(0.f);
+    for (int e = tid; e < 2 * kTile * pad; e += blockDim.x) ks[(e / pad) * ld + D + e % pad] = __float2bfloat16_rn(0.f);
+    for (int e = tid; e < 2 * kRows * PLD; e += blockDim.x) ps[e] = __float2bfloat16_rn(0.f);
   }
   __syncthreads();
 
