@@ -458,7 +458,7 @@ class Ops:
                 tensor = _Lib(load_library("latent_tensor.cu"))
                 self._latent_tensor = tensor.function(
                     "cie_latent_attention_tensor",
-                    [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, v, v])
+                    [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, v, v])
                 self._latent_tensor_supports = tensor.handle.cie_latent_attention_tensor_supports
 
     def latent_prepare(self, down: Any, q_out: Any, q_gain: Any, kv_gain: Any, ctx: Any, kv: Any, rotation: Any,
@@ -540,7 +540,9 @@ class Ops:
                                 _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token), _ptr(table),
                                 table.shape[1], kv.num_pages, _ptr(rotation.inv_freq), float(rotation.magnitude),
                                 int(rotation.interleaved), int(rotation.dims), _ptr(sink), tokens, heads, rank, rot,
-                                kv.page_size, float(scale), range_keys, ranges, _ptr(self.error_word), self.stream)
+                                kv.page_size, float(scale), range_keys, ranges,
+                                0 if os.environ.get("CIE_LATENT_PAIRS", "1") == "0" else 1, _ptr(self.error_word),
+                                self.stream)
             if ranges > 1:
                 self._latent_merge(_ptr(scratch), _ptr(out), _ptr(ctx.positions), _ptr(sink), tokens, heads, rank,
                                    range_keys, ranges, self.stream)
