@@ -252,6 +252,7 @@ __global__ void head_scatter_kernel(const __nv_bfloat16* __restrict__ y, TO* __r
 // rotated.  ranges == 1: the normalised sum goes to out [T, heads, rank]; else the CTA leaves
 // (maximum, sum, unnormalised latent sum) in part [T, heads, ranges, rank + 2].
 constexpr int kAttnHeads = 8;
+constexpr int kLatentMaxRank = 1024;
 
 __host__ __device__ __forceinline__ size_t latent_row_floats(int rank, int rot) { return (size_t)((rank + rot) | 1); }
 
@@ -303,7 +304,7 @@ latent_attention_kernel(const float* __restrict__ q_abs, const float* __restrict
     for (int i = rot_dims + lane; i < rot; i += 32) qs[warp * D + rank + i] = qr[i];
   }
 
-  constexpr int kMaxCols = 16;                          // latent columns of a lane: rank <= 512
+  constexpr int kMaxCols = kLatentMaxRank / 32;         // latent columns of a lane
   float acc[kMaxCols];
 #pragma unroll
   for (int i = 0; i < kMaxCols; ++i) acc[i] = 0.f;
@@ -494,7 +495,7 @@ extern "C" int cie_latent_merge(const float* part, float* out, const int* positi
   return 0;
 }
 
-extern "C" int cie_latent_attention_max_rank() { return 512; }
+extern "C" int cie_latent_attention_max_rank() { return cie::kLatentMaxRank; }
 
 extern "C" int cie_latent_attention(const float* q_abs, const float* q_raw, int q_raw_stride, int q_raw_head,
                                     float* out, float* part, const void* c_pool, const void* r_pool,
@@ -505,7 +506,7 @@ extern "C" int cie_latent_attention(const float* q_abs, const float* q_raw, int 
                                     int dtype, int* err, void* stream) {
   using namespace cie;
   if (tokens <= 0) return 0;
-  if (rank > 512) CIE_FAIL("latent_attention: latent size %d is above 512", rank);
+  if (rank > kLatentMaxRank) CIE_FAIL("latent_attention: latent size %d is above %d", rank, kLatentMaxRank);
   if (range_keys < 32 || range_keys % 32) CIE_FAIL("latent_attention: key ranges are multiples of 32, got %d", range_keys);
   if (ranges < 1 || ranges > 65535) CIE_FAIL("latent_attention: %d key ranges", ranges);
   if (ranges > 1 && !part) CIE_FAIL("latent_attention: key ranges need scratch memory");

@@ -528,10 +528,16 @@ class Ops:
         groups = -(-heads // (16 if tensor else 8))
         ranges, range_keys, scratch = 1, 1 << 30, None
         if tokens * groups < self.sm_count:
-            range_keys = 128
-            ranges = max(1, -(-table.shape[1] * kv.page_size // range_keys))
+            # about two CTAs an SM: ranges of a multiple of 128 keys, counted over the longest context the tables hold
+            longest = table.shape[1] * kv.page_size
+            wanted = -(-2 * self.sm_count // (tokens * groups))
+            range_keys = max(128, (-(-longest // wanted) + 127) // 128 * 128)
+            ranges = max(1, -(-longest // range_keys))
         if ranges > 1:
-            scratch = self.scratch("latent.ranges", tokens * heads * ranges * (rank + 2))
+            # tokens x groups x ranges stays within a few CTAs an SM, which bounds the scratch memory whatever the
+            # step: made once at that size, it need not grow under a captured graph
+            reserve = 8 * self.sm_count * (heads // groups + 1) * (rank + 2)
+            scratch = self.scratch("latent.ranges", tokens * heads * ranges * (rank + 2), reserve=reserve)
         else:
             ranges, range_keys = 1, 1 << 30
         self.launches += 2 if ranges > 1 else 1

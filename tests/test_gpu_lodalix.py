@@ -417,6 +417,38 @@ def test_attention_over_latent_rows_with_one_key_that_stands_out(dtype, with_sin
             assert (last[1] - latent_rows[n - 1].double()).abs().max() < 0.05 + (0.2 if with_sink else 0.0)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rank,rot_dim,heads", [(512, 64, 16), (640, 16, 3), (1024, 8, 2), (72, 24, 20)])
+def test_attention_over_wide_latents_and_many_heads(dtype, rank, rot_dim, heads):
+    """Latents at and above what the tensor-core kernel takes, more heads than one tile of 16 rows, a
+    portion whose tokens pair up in CTAs next to single queries of other requests."""
+    rt = runtime(dtype)
+    page, scale = 16, 1.5 / rank ** 0.5
+    rot = rotary(rot_dim, 1000.0)
+    lengths, contexts = [1, 1, 71, 2], [130, 0, 0, 64]
+    tokens = sum(lengths)
+    ctx, kv, table = fake_step(lengths, contexts, page, rt.dtype, rank, rot_dim, seed=3)
+    rows = [(rand(c + n, rank, seed=10 + r).to(rt.dtype), rand(c + n, rot_dim, seed=20 + r).to(rt.dtype))
+            for r, (n, c) in enumerate(zip(lengths, contexts))]
+    for r, (latent_rows, key_rows) in enumerate(rows):
+        for p in range(latent_rows.shape[0]):
+            kv.k[int(table[r, p // page]), 0, p % page] = latent_rows[p].cuda()
+            kv.v[int(table[r, p // page]), 0, p % page] = key_rows[p].cuda()
+    q_latent, q_raw = rand(tokens, heads * rank, seed=5), rand(tokens, heads * rot_dim, seed=6)
+    sink = rand(heads, seed=7)
+    out = torch.zeros(tokens, heads * rank, dtype=torch.float32).cuda()
+    rt.ops.latent_attention(q_latent.cuda(), q_raw.cuda(), rot_dim, out, ctx, kv, rotation_of(rot, "interleaved"), sink.cuda(),
+                            heads, rank, rot_dim, scale)
+    rt.ops.check_errors()
+    row = 0
+    for r, (n, c) in enumerate(zip(lengths, contexts)):
+        for position in range(c, c + n):
+            rotated = plain.rotate(q_raw[row].view(1, heads, rot_dim).double(), torch.tensor([position]), rot, "interleaved")[0]
+            want = attention_oracle(q_latent[row].view(heads, rank), rotated, rows[r][0], rows[r][1], position, scale, sink)
+            close(out[row].view(heads, rank), want, dtype, scale=1.0, loose=4e-2)
+            row += 1
+
+
 @pytest.mark.parametrize("first_lengths", [[13, 1, 6], [40, 3, 33]])      # the second: the two-kernel form for portions
 @pytest.mark.parametrize("dim", [1, 7, 16, 33, 64, 100, 128])
 def test_delta_scan_carries_its_state_between_steps_and_leaves_padding_rows_alone(dim, first_lengths):
