@@ -679,7 +679,8 @@ def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int, only: st
                 decode_tokens_per_s=round(batch / decode_ms * 1e3, 1), decode_launches=decode_launches)
 
 
-def run_zisesun(args: argparse.Namespace, design: str = "zisesun") -> int:
+def run_design(args: argparse.Namespace, design: str = "zisesun") -> int:
+    """A second or third design at its sizes beside the Qwen2 dense shape of equal size."""
     import torch
 
     sizes = {"zisesun": ZISESUN_SIZES, "lodalix": LODALIX_SIZES}[design]
@@ -778,7 +779,7 @@ def main() -> int:
     if args.impl == "reference":
         return run_reference(args)
     if args.config in ("zisesun", "lodalix"):
-        return run_zisesun(args, args.config)
+        return run_design(args, args.config)
     if args.config != "3b":
         return run_other_config(args)
     return run_own(args)

@@ -71,3 +71,6 @@ class Runtime:
         if max_tokens and max_requests:
             bucket = 1 << (min(max_requests, max_tokens) - 1).bit_length()
         self.workspace = Workspace(self.device, max(max_tokens, bucket), bucket)
+        # kernels that keep scratch memory by the token make it for the largest step at first use, so that
+        # it need not grow once a captured graph holds its address
+        self.ops.max_rows = self.workspace.max_rows

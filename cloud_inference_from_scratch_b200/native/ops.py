@@ -82,6 +82,7 @@ class Ops:
             raise KernelError(f"unknown gemm mode {self.gemm_mode!r}")
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self.max_rows = 0             # most tokens of a step, if the runtime knows (0: not known)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
         v, i, f = c_void_p, c_int, c_float
@@ -461,6 +462,11 @@ class Ops:
                     [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, v, v])
                 self._latent_tensor_supports = tensor.handle.cie_latent_attention_tensor_supports
 
+    def require_latent(self) -> int:
+        """Builds, at model set-up, the kernels of attention over a cached latent; returns the largest latent they take."""
+        self._load_latent()
+        return self.latent_max_rank
+
     def latent_prepare(self, down: Any, q_out: Any, q_gain: Any, kv_gain: Any, ctx: Any, kv: Any, rotation: Any,
                        q_rank: int, rank: int, rot: int, eps: float, has_kv: bool, write_cache: bool) -> None:
         """Per token of ``down`` (float32 [T, q_rank (+ rank + rot)]): the query latent divided by its
@@ -494,9 +500,12 @@ class Ops:
         if (self.code == BF16 and tokens > STREAM_MAX_ROWS and weight.dtype == self.torch.bfloat16
                 and os.environ.get("CIE_HEAD_BATCHED", "1") != "0"):
             torch = self.torch
-            rows = self.scratch("head.rows", (heads * tokens * depth + 1) // 2).view(torch.bfloat16)
+            most = max(tokens, self.max_rows)
+            rows = self.scratch(f"head.rows.{heads}x{depth}", (heads * tokens * depth + 1) // 2, reserve=(heads * most * depth + 1) // 2)
+            rows = rows.view(torch.bfloat16)
             rows = rows[: heads * tokens * depth].view(heads, tokens, depth)
-            result = self.scratch("head.result", (heads * tokens * width + 1) // 2).view(torch.bfloat16)
+            result = self.scratch(f"head.result.{heads}x{width}", (heads * tokens * width + 1) // 2, reserve=(heads * most * width + 1) // 2)
+            result = result.view(torch.bfloat16)
             result = result[: heads * tokens * width].view(heads, tokens, width)
             self.launches += 3
             self._head_gather(_ptr(x), x.stride(0), x_head, _ptr(rows), tokens, heads, depth, self.stream)
@@ -537,7 +546,7 @@ class Ops:
             # tokens x groups x ranges stays within a few CTAs an SM, which bounds the scratch memory whatever the
             # step: made once at that size, it need not grow under a captured graph
             reserve = 8 * self.sm_count * (heads // groups + 1) * (rank + 2)
-            scratch = self.scratch("latent.ranges", tokens * heads * ranges * (rank + 2), reserve=reserve)
+            scratch = self.scratch(f"latent.ranges.{heads}x{rank}", tokens * heads * ranges * (rank + 2), reserve=reserve)
         else:
             ranges, range_keys = 1, 1 << 30
         self.launches += 2 if ranges > 1 else 1
@@ -575,6 +584,11 @@ class Ops:
             self.delta_max_dim = int(lib.handle.cie_delta_max_dim())
             self._delta_lib = lib
 
+    def require_delta(self) -> int:
+        """Builds, at model set-up, the kernels of the generalized delta rule; returns the largest head size they take."""
+        self._load_delta()
+        return self.delta_max_dim
+
     def tanh_rows(self, x: Any, out: Any) -> None:
         """out = tanh(x) for float32 ``x`` (may be a view of columns), rounded to ``out``'s dtype."""
         self._flush()
@@ -596,7 +610,9 @@ class Ops:
         r_off, k_off, v_off, a_off = offsets
         tokens = proj.shape[0]
         if tokens >= 8 * ctx.num_requests and os.environ.get("CIE_DELTA_STREAM", "1") != "0":
-            packed = self.scratch("delta.packed", int(self._delta_lib.handle.cie_delta_stream_floats(tokens, heads, dim)))
+            floats = self._delta_lib.handle.cie_delta_stream_floats
+            packed = self.scratch(f"delta.packed.{heads}x{dim}", int(floats(tokens, heads, dim)),
+                                  reserve=int(floats(max(tokens, self.max_rows), heads, dim)))
             self.launches += 2
             self._delta_stream(_ptr(proj), proj.stride(0), r_off, k_off, v_off, a_off, _ptr(decay), decay.stride(0),
                                _ptr(decay_bias), _ptr(removal_bias), _ptr(packed), _ptr(out), out.stride(0), _ptr(state),

@@ -56,9 +56,9 @@ class GeneralDelta(Mixer):
 
         self.runtime = runtime
         ops, n = runtime.ops, self.names
-        ops._load_delta()
-        if self.head_dim > ops.delta_max_dim:
-            raise ValueError(f"the delta-rule kernel takes heads of up to {ops.delta_max_dim}, got {self.head_dim}")
+        largest = ops.require_delta()
+        if self.head_dim > largest:
+            raise ValueError(f"the delta-rule kernel takes heads of up to {largest}, got {self.head_dim}")
         self.rank = int(tensors[n["w1"]].shape[0])
         if tensors[n["w2"]].shape[1] != self.rank:
             raise ValueError("the two decay projections disagree about their inner width")

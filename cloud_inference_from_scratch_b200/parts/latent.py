@@ -87,9 +87,9 @@ class LatentAttention(Mixer):
 
         self.runtime = runtime
         ops, n, heads = runtime.ops, self.names, self.num_heads
-        ops._load_latent()
-        if self.kv_rank > ops.latent_max_rank:
-            raise ValueError(f"latent attention kernels take a latent of up to {ops.latent_max_rank}, got {self.kv_rank}")
+        largest = ops.require_latent()
+        if self.kv_rank > largest:
+            raise ValueError(f"latent attention kernels take a latent of up to {largest}, got {self.kv_rank}")
         # one product for everything that reads h: query latent, then latent and key part, then the gate
         stacked = [tensors[n["dq"]]]
         if not self.shares_cache:

@@ -573,13 +573,18 @@ def test_parts_alone_against_the_plain_sublayers(dtype):
 
 # ------------------------------------------------------------------ the public entry point
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_greedy_generation_through_the_engine(folders, dtype):
+@pytest.mark.parametrize("chunk,active", [(8, 3), (24, 1)])
+def test_greedy_generation_through_the_engine(folders, dtype, chunk, active):
+    """Through the scheduler, the runner's captured decode steps and the sampler.  The second setting runs the
+    requests one after the other with portions of 24 tokens: the long prompts come when decode steps have
+    been captured already, so whatever their kernels keep by the token must have its full size by then."""
     from cloud_inference_from_scratch_b200 import generate
 
     raw, tensors = plain.read_folder(folders.get("mixed", dtype))
     prompts = [random_tokens(raw["vocab"], n, 100 + n) for n in (1, 9, 30, 17)]
     results = generate(folders.get("mixed", dtype), prompts, max_output_tokens=12, dtype=dtype, block_size=4,
-                       kv_cache_blocks=40, prefill_chunk_size=8, max_batched_tokens=20, max_active_sequences=3)
+                       kv_cache_blocks=40, prefill_chunk_size=chunk, max_batched_tokens=chunk + 12,
+                       max_active_sequences=active)
     for prompt, result in zip(prompts, results):
         got = result.token_ids
         assert len(got) == 12
