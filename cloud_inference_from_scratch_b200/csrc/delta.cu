@@ -23,7 +23,9 @@ CIE_DEFINE_LAST_ERROR()
 namespace cie {
 
 constexpr int kDeltaLanes = 8;         // lanes that share a value column
-constexpr int kDeltaMaxDim = 128;
+constexpr int kDeltaMaxDim = 256;       // largest head of the scan kernel
+constexpr int kDeltaBlockColumns = 128;  // value columns of a block (heads above that take several blocks)
+constexpr int kDeltaStreamMaxDim = 128; // largest head of the stream kernel (a column's rows are one thread's registers)
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 
@@ -39,12 +41,13 @@ __global__ void tanh_rows_kernel(const float* __restrict__ x, int stride, T* __r
   out[e] = from_float<T>(tanhf(x[t * stride + i]));
 }
 
-// grid (requests, heads); kDeltaLanes * dim threads rounded up to whole warps.
+// grid (requests, heads, blocks of kDeltaBlockColumns value columns); kDeltaLanes threads a column, rounded up
+// to whole warps.  Every block stages all rows of k, r and the rates; it keeps only its own columns of S.
 // proj: float32 rows [r | k | v | ... ] with heads side by side inside each part; `r_off`, `k_off`, `v_off`,
 // `a_off` are the first columns of r, k, v and the removal projection; `decay` is its own tensor
 // [T, heads * dim] (the decay projection, before its bias).  R = rows of a lane.
 template <int R>
-__global__ void __launch_bounds__(kDeltaLanes * kDeltaMaxDim)
+__global__ void __launch_bounds__(kDeltaLanes * kDeltaBlockColumns)
 delta_scan_kernel(const float* __restrict__ proj, int proj_stride, int r_off, int k_off, int v_off, int a_off,
                   const float* __restrict__ decay, int decay_stride, const float* __restrict__ decay_bias,
                   const float* __restrict__ removal_bias, float* __restrict__ out, int out_stride,
@@ -56,7 +59,7 @@ delta_scan_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
   pdl_trigger();
   const int request = blockIdx.x, head = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31;
-  const int column = tid / kDeltaLanes, part = tid % kDeltaLanes;
+  const int column = blockIdx.z * kDeltaBlockColumns + tid / kDeltaLanes, part = tid % kDeltaLanes;
   const bool live = column < dim;
   const int slot = slots[request];
   if (slot < 0 || slot >= max_slots) {
@@ -71,9 +74,9 @@ delta_scan_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
     const int row = part * R + i;
     s[i] = (live && row < dim) ? s_base[(size_t)row * dim + column] : 0.f;
   }
-  if (tid < kPad) {
+  for (int i = tid; i < kPad; i += blockDim.x) {
 #pragma unroll
-    for (int b = 0; b < 2; ++b) w_s[b][tid] = au_s[b][tid] = u_s[b][tid] = k_s[b][tid] = r_s[b][tid] = 0.f;
+    for (int b = 0; b < 2; ++b) w_s[b][i] = au_s[b][i] = u_s[b][i] = k_s[b][i] = r_s[b][i] = 0.f;
   }
   const int base = head * dim;
   const float w0 = tid < dim ? decay_bias[base + tid] : 0.f;
@@ -203,7 +206,7 @@ __device__ __forceinline__ void delta_cp_async16(void* dst, const void* src) {
 // same address for the whole warp (one shared-memory wavefront a load, where lanes that share a column
 // read eight different places), and no sum crosses lanes.  P = rows as padded (32, 64 or 128).
 template <int P>
-__global__ void __launch_bounds__(kDeltaMaxDim)
+__global__ void __launch_bounds__(kDeltaStreamMaxDim)
 delta_stream_kernel(const float* __restrict__ packed, float* __restrict__ out, int out_stride, float* __restrict__ state,
                     const int* __restrict__ query_start, const int* __restrict__ slots,
                     const int* __restrict__ request_active, int tokens, int heads, int dim, int max_slots, int* err) {
@@ -313,6 +316,7 @@ group_gate_norm_kernel(const float* __restrict__ o, int o_stride, const float* _
   else CIE_FAIL("%s: unknown dtype code %d", name, (code));
 
 extern "C" int cie_delta_max_dim() { return cie::kDeltaMaxDim; }
+extern "C" int cie_delta_stream_max_dim() { return cie::kDeltaStreamMaxDim; }
 
 extern "C" int cie_tanh_rows(const float* x, int stride, void* out, int rows, int width, int dtype, void* stream) {
   using namespace cie;
@@ -333,15 +337,17 @@ extern "C" int cie_delta_scan(const float* proj, int proj_stride, int r_off, int
   using namespace cie;
   if (requests <= 0) return 0;
   if (dim < 1 || dim > kDeltaMaxDim) CIE_FAIL("delta_scan: head size %d is outside 1..%d", dim, kDeltaMaxDim);
-  const int threads = (kDeltaLanes * dim + 31) / 32 * 32;
-  const dim3 grid(requests, heads);
+  const int columns = dim < kDeltaBlockColumns ? dim : kDeltaBlockColumns;
+  const int threads = (kDeltaLanes * columns + 31) / 32 * 32;
+  const dim3 grid(requests, heads, (dim + kDeltaBlockColumns - 1) / kDeltaBlockColumns);
 #define CIE_DELTA_SCAN(R)                                                                                        \
   CIE_LAUNCH("delta_scan", delta_scan_kernel<R>, grid, dim3(threads), 0, (cudaStream_t)stream, proj, proj_stride, \
              r_off, k_off, v_off, a_off, decay, decay_stride, decay_bias, removal_bias, out, out_stride, state,  \
              query_start, slots, request_active, heads, dim, max_slots, err)
   if (dim <= 32) { CIE_DELTA_SCAN(4); }
   else if (dim <= 64) { CIE_DELTA_SCAN(8); }
-  else { CIE_DELTA_SCAN(16); }
+  else if (dim <= 128) { CIE_DELTA_SCAN(16); }
+  else { CIE_DELTA_SCAN(32); }
 #undef CIE_DELTA_SCAN
   return 0;
 }
@@ -359,7 +365,7 @@ extern "C" int cie_delta_stream(const float* proj, int proj_stride, int r_off, i
                                 int requests, int heads, int dim, int max_slots, int* err, void* stream) {
   using namespace cie;
   if (requests <= 0 || tokens <= 0) return 0;
-  if (dim < 1 || dim > kDeltaMaxDim) CIE_FAIL("delta_stream: head size %d is outside 1..%d", dim, kDeltaMaxDim);
+  if (dim < 1 || dim > kDeltaStreamMaxDim) CIE_FAIL("delta_stream: head size %d is outside 1..%d", dim, kDeltaStreamMaxDim);
   const int pad = dim <= 32 ? 32 : dim <= 64 ? 64 : 128;
   CIE_LAUNCH("delta_prepare", delta_prepare_kernel, dim3(tokens, heads), dim3(32), 0, (cudaStream_t)stream, proj,
              proj_stride, r_off, k_off, v_off, a_off, decay, decay_stride, decay_bias, removal_bias, packed, tokens, heads,

@@ -582,6 +582,7 @@ class Ops:
                 "cie_delta_stream", [v, i, i, i, i, i, v, i, v, v, v, v, i, v, v, v, v, i, i, i, i, i, v, v])
             lib.handle.cie_delta_stream_floats.restype = ctypes.c_longlong
             self.delta_max_dim = int(lib.handle.cie_delta_max_dim())
+            self.delta_stream_max_dim = int(lib.handle.cie_delta_stream_max_dim())
             self._delta_lib = lib
 
     def require_delta(self) -> int:
@@ -609,7 +610,8 @@ class Ops:
         self._load_delta()
         r_off, k_off, v_off, a_off = offsets
         tokens = proj.shape[0]
-        if tokens >= 8 * ctx.num_requests and os.environ.get("CIE_DELTA_STREAM", "1") != "0":
+        if (tokens >= 8 * ctx.num_requests and dim <= self.delta_stream_max_dim
+                and os.environ.get("CIE_DELTA_STREAM", "1") != "0"):
             floats = self._delta_lib.handle.cie_delta_stream_floats
             packed = self.scratch(f"delta.packed.{heads}x{dim}", int(floats(tokens, heads, dim)),
                                   reserve=int(floats(max(tokens, self.max_rows), heads, dim)))

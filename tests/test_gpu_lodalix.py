@@ -450,7 +450,7 @@ def test_attention_over_wide_latents_and_many_heads(dtype, rank, rot_dim, heads)
 
 
 @pytest.mark.parametrize("first_lengths", [[13, 1, 6], [40, 3, 33]])      # the second: the two-kernel form for portions
-@pytest.mark.parametrize("dim", [1, 7, 16, 33, 64, 100, 128])
+@pytest.mark.parametrize("dim", [1, 7, 16, 33, 64, 100, 128, 160, 256])
 def test_delta_scan_carries_its_state_between_steps_and_leaves_padding_rows_alone(dim, first_lengths):
     rt = runtime("float32")
     heads = 3
